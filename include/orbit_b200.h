@@ -1,0 +1,181 @@
+/*
+ * orbit_b200 -- C ABI of the B200 (sm_100a) OrbitQuant quantized-linear forward.
+ *
+ * Every entry point takes plain device pointers, sizes and a CUDA stream
+ * (a cudaStream_t passed as void*; NULL = the legacy default stream).  All pointers are
+ * DEVICE pointers owned by the caller and must stay alive until the stream has run the
+ * work.  Unless an entry point's comment says otherwise the library allocates nothing,
+ * never synchronises the host with the device and keeps no device state of its own, so
+ * every call may be captured into a CUDA graph.
+ *
+ * Return value: 0 on success, a negative oq_status otherwise; oq_last_error() then holds
+ * a message for the calling thread.  The host binding turns OQ_ERR_INVALID into the
+ * ValueError / RuntimeError the reference raises for the same misuse.
+ *
+ * Citations name the reference interface each entry point replaces, as path:line inside
+ * the reference project (iamwavecut/OrbitQuant v0.9.0).
+ */
+#ifndef ORBIT_B200_H_
+#define ORBIT_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define OQ_ABI_VERSION 1
+
+/* Element types of activations / outputs / bias. */
+#define OQ_DTYPE_F32 0
+#define OQ_DTYPE_F16 1
+#define OQ_DTYPE_BF16 2
+
+typedef enum oq_status {
+  OQ_OK = 0,
+  OQ_ERR_INVALID = -1,     /* bad argument (shape, dtype, bits, alignment, null pointer)   */
+  OQ_ERR_UNSUPPORTED = -2, /* valid request this build has no kernel for                   */
+  OQ_ERR_CUDA = -3,        /* a CUDA runtime / driver call failed                          */
+  OQ_ERR_WORKSPACE = -4,   /* caller's workspace is smaller than oq_*_workspace_bytes says */
+  OQ_ERR_DEVICE = -5       /* not an sm_100 device                                         */
+} oq_status;
+
+/* Arithmetic of the weight operand.
+ *   OQ_WEIGHT_CENTROID  : the contraction uses the codebook centroid itself (fp32 on the
+ *                         CUDA-core kernels, fp16(centroid * 2^8) on the tensor-core
+ *                         kernel) and multiplies the sum by row_norm[n] afterwards -- the
+ *                         arithmetic of the reference's fp32-centroid CPU kernels
+ *                         (packed_matmul_scalar.cpp:46-74, packed_matmul_x86.cpp,
+ *                         packed_matmul_x86_avx512.cpp:200-546).
+ *   OQ_WEIGHT_BF16_SCALED: the contraction uses bf16(centroid * row_norm[n]) -- the
+ *                         arithmetic of the reference's AVX512-BF16 W4 kernel
+ *                         (packed_matmul_x86_avx512.cpp:548-699) and of its CUDA wmma
+ *                         kernels (packed_matmul.cu:86-125).
+ *   OQ_WEIGHT_AUTO      : OQ_WEIGHT_CENTROID. */
+#define OQ_WEIGHT_AUTO 0
+#define OQ_WEIGHT_CENTROID 1
+#define OQ_WEIGHT_BF16_SCALED 2
+
+/* Kernel selection for oq_matmul_packed_weight / oq_linear_forward.  AUTO picks by shape:
+ * rows <= 16 -> the streaming small-rows kernel; otherwise the tcgen05 kernel when the
+ * shape qualifies (see oq_gemm_tcgen05_supported), else the general tiled kernel. */
+#define OQ_KERNEL_AUTO 0
+#define OQ_KERNEL_SMALL_ROWS 1
+#define OQ_KERNEL_TILED 2
+#define OQ_KERNEL_TCGEN05 3
+
+int oq_abi_version(void);
+const char *oq_last_error(void);
+
+/* Number of kernels this library has launched from the calling process since load
+ * (monotonic; used by the benchmark to report its own launch count). */
+uint64_t oq_launch_count(void);
+
+/* ---- bit stream --------------------------------------------------------------------- */
+
+/* Unpack `count` little-endian `bits`-wide fields of `packed` into one byte each.
+ * Replaces unpack_lowbit on CUDA tensors (src/orbitquant/packing/bitpack.py:63-97,
+ * src/orbitquant/kernels/triton_cuda.py:879-923).  Bit-exact. */
+int oq_unpack_lowbit(const uint8_t *packed, int bits, int64_t count, uint8_t *values,
+                     void *stream);
+
+/* Inverse of oq_unpack_lowbit; writes ceil(count*bits/8) bytes.  Replaces pack_lowbit on
+ * CUDA tensors (bitpack.py:49-60).  Bit-exact. */
+int oq_pack_lowbit(const uint8_t *values, int bits, int64_t count, uint8_t *packed,
+                   void *stream);
+
+/* Dense weight W[n,k] = f32(row_norm[n]) * centroid[idx[n,k]], written as `out_dtype`.
+ * Replaces OrbitQuantLinear._dequantize_weight on CUDA
+ * (src/orbitquant/layers.py:1001-1070, triton_cuda.py:524-547). */
+int oq_dequantize_weight(const uint8_t *packed, int bits, int64_t out_features,
+                         int64_t in_features, const void *row_norms_bf16,
+                         const float *centroids, void *out, int out_dtype, void *stream);
+
+/* ---- online activation quantisation ------------------------------------------------- */
+
+/* Fused RPBH rotate-and-quantize of `rows` tokens of width `dim`:
+ *   n = ||x||_2 (fp32), s = x[perm]*sign/(n+eps), per-`block` Walsh-Hadamard, /sqrt(block),
+ *   idx = #{boundaries < s}, x_q = centroid[idx]*n rounded to x's dtype.
+ * The fp32 operation order (16-lane fused-multiply-add sum of squares folded 8/4/2/1,
+ * multiply by the reciprocal, radix-2 stages h=1,2,4,...) is the one of the reference's
+ * AVX-512 CPU kernel, so x_q is bit-identical to it.
+ * Replaces quantize_activations_cpu
+ * (native-kernels/orbitquant-packed-matmul/orbitquant_packed_matmul_cpu/
+ *  quantize_activations_cpu.cpp:633-664,731-867; op schema torch-ext/torch_binding.cpp:12-15)
+ * and the CUDA/Triton prologues (orbitquant_packed_matmul_cuda/packed_matmul.cu:581-742,
+ * src/orbitquant/kernels/triton_cuda.py:221-357).
+ *   x, x_q   : [rows, dim] contiguous, dtype x_dtype (x_q may be NULL)
+ *   perm     : int32[dim]; signs: int8[dim] (+1/-1)
+ *   block    : power of two dividing dim
+ *   boundaries: f32[2^bits-1] ascending; centroids: f32[2^bits]
+ *   codes    : optional u8[rows, dim] (the indices); norms: optional f32[rows] */
+int oq_quantize_activations(const void *x, int x_dtype, int64_t rows, int64_t dim,
+                            const int32_t *perm, const int8_t *signs, int64_t block,
+                            const float *boundaries, const float *centroids, int bits,
+                            float eps, void *x_q, uint8_t *codes, float *norms, void *stream);
+
+/* ---- packed-weight matmul ----------------------------------------------------------- */
+
+/* out[m,n] = sum_k x[m,k] * W[n,k] (+ bias[n]),  W decoded on the fly from the packed
+ * `bits`-wide codebook indices (row-major [out_features, in_features] bit stream).
+ * Replaces the native op matmul_packed_weight
+ * (schema torch-ext/torch_binding.cpp:9-11; CUDA host packed_matmul.cu:1335-1713;
+ *  CPU packed_matmul_cpu.cpp:115-201; Python wrapper
+ *  torch-ext/orbitquant_packed_matmul/__init__.py:109-160).
+ *   x        : [rows, in_features] contiguous, dtype `dtype` (the quantised activations)
+ *   packed   : u8, at least ceil(out_features*in_features*bits/8) bytes (packed_bytes is
+ *              checked, as the reference checks numel)
+ *   row_norms: bf16[out_features]; centroids: f32[2^bits]
+ *   bias     : NULL or [out_features] of dtype `bias_dtype`
+ *   out      : [rows, out_features] contiguous, dtype `dtype`
+ *   workspace: see oq_matmul_workspace_bytes (may be NULL when that returns 0) */
+int oq_matmul_packed_weight(void *out, const void *x, int dtype, int64_t rows,
+                            int64_t in_features, int64_t out_features, const uint8_t *packed,
+                            int64_t packed_bytes, int bits, const void *row_norms_bf16,
+                            const float *centroids, const void *bias, int bias_dtype,
+                            int weight_mode, int kernel, void *workspace,
+                            size_t workspace_bytes, void *stream);
+
+size_t oq_matmul_workspace_bytes(int64_t rows, int64_t in_features, int64_t out_features,
+                                 int bits, int dtype, int weight_mode, int kernel);
+
+/* 1 when the tcgen05/TMEM kernel can run this problem (bf16, W4, in_features % 64 == 0,
+ * 16-byte aligned rows), else 0. */
+int oq_gemm_tcgen05_supported(int64_t rows, int64_t in_features, int64_t out_features,
+                              int bits, int dtype, int weight_mode);
+
+/* ---- the whole quantized-linear forward --------------------------------------------- */
+
+/* y = OrbitQuantLinear(x): oq_quantize_activations into workspace, then
+ * oq_matmul_packed_weight.  Replaces OrbitQuantLinear._forward_impl on CUDA
+ * (src/orbitquant/layers.py:1079-1455), i.e. the body of the custom op
+ * orbitquant::packed_linear_forward (layers.py:59-72).
+ * The workspace (oq_linear_workspace_bytes) holds the quantised activations
+ * [rows, in_features] of x's dtype plus whatever the chosen matmul kernel needs. */
+int oq_linear_forward(void *out, const void *x, int dtype, int64_t rows, int64_t in_features,
+                      int64_t out_features, const uint8_t *packed, int64_t packed_bytes,
+                      int weight_bits, const void *row_norms_bf16, const float *weight_centroids,
+                      const void *bias, int bias_dtype, const int32_t *perm,
+                      const int8_t *signs, int64_t block, const float *act_boundaries,
+                      const float *act_centroids, int act_bits, float eps, int weight_mode,
+                      int kernel, void *workspace, size_t workspace_bytes, void *stream);
+
+size_t oq_linear_workspace_bytes(int64_t rows, int64_t in_features, int64_t out_features,
+                                 int weight_bits, int dtype, int weight_mode, int kernel);
+
+/* ---- device status ------------------------------------------------------------------- */
+
+/* Every wait inside the tcgen05 kernel (on an mbarrier) is bounded; a wait that gives up
+ * records a non-zero code in a per-device status word, releases its tensor memory and
+ * returns instead of hanging.  *status receives that word (0 = every wait completed).
+ * This call copies from the device and therefore synchronises; it is meant for tests and
+ * debugging, not for the forward path.  No counterpart in the reference (its kernels have
+ * no device-side waits). */
+int oq_gemm_device_status(int *status);
+int oq_gemm_clear_device_status(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* ORBIT_B200_H_ */

@@ -1,0 +1,256 @@
+// extern "C" surface of liborbit_b200.so: argument validation, kernel choice, status.
+#include <cstring>
+
+#include "common.cuh"
+
+namespace oq {
+
+thread_local char g_last_error[512] = "";
+std::atomic<uint64_t> g_launch_count{0};
+
+int fail(int status, const char *format, ...) {
+  va_list args;
+  va_start(args, format);
+  vsnprintf(g_last_error, sizeof(g_last_error), format, args);
+  va_end(args);
+  return status;
+}
+
+int launch_rotate_quantize(const void *x, int x_dtype, int64_t rows, int64_t dim,
+                           const int32_t *perm, const int8_t *signs, int64_t block,
+                           const float *boundaries, const float *centroids, int bits, float eps,
+                           void *x_q, uint8_t *codes, float *norms, cudaStream_t stream);
+int launch_tiled_matmul(void *out, const void *x, int dtype, int64_t rows, int64_t in_features,
+                        int64_t out_features, const uint8_t *packed, int bits,
+                        const void *row_norms_bf16, const float *centroids, const void *bias,
+                        int bias_dtype, int weight_mode, cudaStream_t stream);
+int launch_small_rows(void *out, const void *x, int dtype, int64_t rows, int64_t in_features,
+                      int64_t out_features, const uint8_t *packed, int bits,
+                      const void *row_norms_bf16, const float *centroids, const void *bias,
+                      int bias_dtype, int weight_mode, cudaStream_t stream);
+bool small_rows_supported(int64_t rows, int64_t in_features, int64_t out_features, int bits,
+                          int dtype, int weight_mode);
+int launch_unpack(const uint8_t *packed, int bits, int64_t count, uint8_t *values,
+                  cudaStream_t stream);
+int launch_pack(const uint8_t *values, int bits, int64_t count, uint8_t *packed,
+                cudaStream_t stream);
+int launch_dequantize(const uint8_t *packed, int bits, int64_t out_features, int64_t in_features,
+                      const void *row_norms_bf16, const float *centroids, void *out,
+                      int out_dtype, cudaStream_t stream);
+bool tcgen05_gemm_supported(int64_t rows, int64_t in_features, int64_t out_features, int bits,
+                            int dtype, int weight_mode);
+int launch_tcgen05_gemm(void *out, const void *x, int64_t rows, int64_t in_features,
+                        int64_t out_features, const uint8_t *packed, const void *row_norms_bf16,
+                        const float *centroids, const void *bias, int bias_dtype,
+                        cudaStream_t stream);
+int read_gemm_status(int *status);
+int clear_gemm_status();
+
+namespace {
+
+// The kernels are built for sm_100a only; refuse anything else before a launch fails with
+// "no kernel image".
+int check_device() {
+  static thread_local int checked_device = -1;
+  int device = 0;
+  OQ_CHECK_CUDA(cudaGetDevice(&device));
+  if (device == checked_device) {
+    return OQ_OK;
+  }
+  int major = 0;
+  OQ_CHECK_CUDA(cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, device));
+  if (major != 10) {
+    return fail(OQ_ERR_DEVICE, "orbit_b200 kernels are built for sm_100a; device %d is sm_%d", device,
+                major * 10);
+  }
+  checked_device = device;
+  return OQ_OK;
+}
+
+int resolve_weight_mode(int weight_mode) {
+  return weight_mode == OQ_WEIGHT_AUTO ? OQ_WEIGHT_CENTROID : weight_mode;
+}
+
+size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
+
+}  // namespace
+}  // namespace oq
+
+using namespace oq;
+
+extern "C" {
+
+int oq_abi_version(void) { return OQ_ABI_VERSION; }
+
+const char *oq_last_error(void) { return g_last_error; }
+
+uint64_t oq_launch_count(void) { return g_launch_count.load(std::memory_order_relaxed); }
+
+int oq_unpack_lowbit(const uint8_t *packed, int bits, int64_t count, uint8_t *values, void *stream) {
+  OQ_CHECK_ARG(bits >= 1 && bits <= 8, "bits must be in [1, 8]");
+  OQ_CHECK_ARG(count >= 0, "length must be non-negative");
+  if (count == 0) {
+    return OQ_OK;
+  }
+  OQ_CHECK_ARG(packed != nullptr && values != nullptr, "null device pointer");
+  if (int rc = check_device()) {
+    return rc;
+  }
+  return launch_unpack(packed, bits, count, values, static_cast<cudaStream_t>(stream));
+}
+
+int oq_pack_lowbit(const uint8_t *values, int bits, int64_t count, uint8_t *packed, void *stream) {
+  OQ_CHECK_ARG(bits >= 1 && bits <= 8, "bits must be in [1, 8]");
+  OQ_CHECK_ARG(count >= 0, "length must be non-negative");
+  if (count == 0) {
+    return OQ_OK;
+  }
+  OQ_CHECK_ARG(packed != nullptr && values != nullptr, "null device pointer");
+  if (int rc = check_device()) {
+    return rc;
+  }
+  return launch_pack(values, bits, count, packed, static_cast<cudaStream_t>(stream));
+}
+
+int oq_dequantize_weight(const uint8_t *packed, int bits, int64_t out_features, int64_t in_features,
+                         const void *row_norms_bf16, const float *centroids, void *out,
+                         int out_dtype, void *stream) {
+  OQ_CHECK_ARG(bits >= 1 && bits <= 8, "bits must be in [1, 8]");
+  OQ_CHECK_ARG(valid_dtype(out_dtype), "out must be float32, float16, or bfloat16");
+  OQ_CHECK_ARG(out_features >= 0 && in_features >= 0, "negative shape");
+  if (out_features == 0 || in_features == 0) {
+    return OQ_OK;
+  }
+  OQ_CHECK_ARG(packed && row_norms_bf16 && centroids && out, "null device pointer");
+  if (int rc = check_device()) {
+    return rc;
+  }
+  return launch_dequantize(packed, bits, out_features, in_features, row_norms_bf16, centroids, out,
+                           out_dtype, static_cast<cudaStream_t>(stream));
+}
+
+int oq_quantize_activations(const void *x, int x_dtype, int64_t rows, int64_t dim,
+                            const int32_t *perm, const int8_t *signs, int64_t block,
+                            const float *boundaries, const float *centroids, int bits, float eps,
+                            void *x_q, uint8_t *codes, float *norms, void *stream) {
+  if (int rc = check_device()) {
+    return rc;
+  }
+  return launch_rotate_quantize(x, x_dtype, rows, dim, perm, signs, block, boundaries, centroids,
+                                bits, eps, x_q, codes, norms, static_cast<cudaStream_t>(stream));
+}
+
+int oq_gemm_tcgen05_supported(int64_t rows, int64_t in_features, int64_t out_features, int bits,
+                              int dtype, int weight_mode) {
+  return tcgen05_gemm_supported(rows, in_features, out_features, bits, dtype,
+                                resolve_weight_mode(weight_mode))
+             ? 1
+             : 0;
+}
+
+size_t oq_matmul_workspace_bytes(int64_t, int64_t, int64_t, int, int, int, int) { return 0; }
+
+int oq_matmul_packed_weight(void *out, const void *x, int dtype, int64_t rows, int64_t in_features,
+                            int64_t out_features, const uint8_t *packed, int64_t packed_bytes,
+                            int bits, const void *row_norms_bf16, const float *centroids,
+                            const void *bias, int bias_dtype, int weight_mode, int kernel,
+                            void *workspace, size_t workspace_bytes, void *stream) {
+  (void)workspace;
+  (void)workspace_bytes;
+  OQ_CHECK_ARG(bits >= 1 && bits <= 8, "bits must be in [1, 8]");
+  OQ_CHECK_ARG(valid_dtype(dtype), "x must be float32, float16, or bfloat16");
+  OQ_CHECK_ARG(rows >= 0 && in_features > 0 && out_features >= 0, "negative or empty shape");
+  OQ_CHECK_ARG(weight_mode >= OQ_WEIGHT_AUTO && weight_mode <= OQ_WEIGHT_BF16_SCALED,
+               "unknown weight_mode %d", weight_mode);
+  OQ_CHECK_ARG(kernel >= OQ_KERNEL_AUTO && kernel <= OQ_KERNEL_TCGEN05, "unknown kernel %d", kernel);
+  OQ_CHECK_ARG(bias == nullptr || valid_dtype(bias_dtype), "bias must be float32, float16, or bfloat16");
+  const int64_t needed = (out_features * in_features * bits + 7) / 8;
+  OQ_CHECK_ARG(packed_bytes >= needed, "packed weights are too short");
+  if (rows == 0 || out_features == 0) {
+    return OQ_OK;
+  }
+  OQ_CHECK_ARG(out && x && packed && row_norms_bf16 && centroids, "null device pointer");
+  if (int rc = check_device()) {
+    return rc;
+  }
+  const int mode = resolve_weight_mode(weight_mode);
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  int chosen = kernel;
+  if (chosen == OQ_KERNEL_AUTO) {
+    if (rows <= 16 && small_rows_supported(rows, in_features, out_features, bits, dtype, mode)) {
+      chosen = OQ_KERNEL_SMALL_ROWS;
+    } else if (rows > 16 && tcgen05_gemm_supported(rows, in_features, out_features, bits, dtype, mode)) {
+      chosen = OQ_KERNEL_TCGEN05;
+    } else {
+      chosen = OQ_KERNEL_TILED;
+    }
+  }
+  switch (chosen) {
+    case OQ_KERNEL_SMALL_ROWS:
+      if (!small_rows_supported(rows, in_features, out_features, bits, dtype, mode)) {
+        return fail(OQ_ERR_UNSUPPORTED, "the small-rows kernel does not take this problem");
+      }
+      return launch_small_rows(out, x, dtype, rows, in_features, out_features, packed, bits,
+                               row_norms_bf16, centroids, bias, bias_dtype, mode, s);
+    case OQ_KERNEL_TCGEN05:
+      if (!tcgen05_gemm_supported(rows, in_features, out_features, bits, dtype, mode)) {
+        return fail(OQ_ERR_UNSUPPORTED,
+                    "the tcgen05 kernel takes bf16 activations, 4-bit weights, in_features %% 64 == 0 "
+                    "and the centroid weight mode");
+      }
+      return launch_tcgen05_gemm(out, x, rows, in_features, out_features, packed, row_norms_bf16,
+                                 centroids, bias, bias_dtype, s);
+    default:
+      return launch_tiled_matmul(out, x, dtype, rows, in_features, out_features, packed, bits,
+                                 row_norms_bf16, centroids, bias, bias_dtype, mode, s);
+  }
+}
+
+size_t oq_linear_workspace_bytes(int64_t rows, int64_t in_features, int64_t out_features,
+                                 int weight_bits, int dtype, int weight_mode, int kernel) {
+  const size_t xq = align_up(static_cast<size_t>(rows) * in_features * dtype_size(dtype), 256);
+  return xq + oq_matmul_workspace_bytes(rows, in_features, out_features, weight_bits, dtype,
+                                        weight_mode, kernel);
+}
+
+int oq_linear_forward(void *out, const void *x, int dtype, int64_t rows, int64_t in_features,
+                      int64_t out_features, const uint8_t *packed, int64_t packed_bytes,
+                      int weight_bits, const void *row_norms_bf16, const float *weight_centroids,
+                      const void *bias, int bias_dtype, const int32_t *perm, const int8_t *signs,
+                      int64_t block, const float *act_boundaries, const float *act_centroids,
+                      int act_bits, float eps, int weight_mode, int kernel, void *workspace,
+                      size_t workspace_bytes, void *stream) {
+  OQ_CHECK_ARG(valid_dtype(dtype), "x must be float32, float16, or bfloat16");
+  OQ_CHECK_ARG(rows >= 0 && in_features > 0 && out_features >= 0, "negative or empty shape");
+  if (rows == 0 || out_features == 0) {
+    return OQ_OK;
+  }
+  const size_t need = oq_linear_workspace_bytes(rows, in_features, out_features, weight_bits, dtype,
+                                                weight_mode, kernel);
+  if (workspace == nullptr || workspace_bytes < need) {
+    return fail(OQ_ERR_WORKSPACE, "workspace of %zu bytes given, %zu needed", workspace_bytes, need);
+  }
+  OQ_CHECK_ARG(aligned16(workspace), "workspace must be 16-byte aligned");
+  int rc = oq_quantize_activations(x, dtype, rows, in_features, perm, signs, block, act_boundaries,
+                                   act_centroids, act_bits, eps, workspace, nullptr, nullptr, stream);
+  if (rc != OQ_OK) {
+    return rc;
+  }
+  const size_t xq = align_up(static_cast<size_t>(rows) * in_features * dtype_size(dtype), 256);
+  return oq_matmul_packed_weight(out, workspace, dtype, rows, in_features, out_features, packed,
+                                 packed_bytes, weight_bits, row_norms_bf16, weight_centroids, bias,
+                                 bias_dtype, weight_mode, kernel,
+                                 static_cast<unsigned char *>(workspace) + xq, workspace_bytes - xq,
+                                 stream);
+}
+
+// Status word of the tcgen05 kernel's bounded waits (0 = every wait completed).  Reading
+// it synchronises the host with the device; it is meant for tests and debugging.
+int oq_gemm_device_status(int *status) {
+  OQ_CHECK_ARG(status != nullptr, "null pointer");
+  return read_gemm_status(status);
+}
+
+int oq_gemm_clear_device_status(void) { return clear_gemm_status(); }
+
+}  // extern "C"

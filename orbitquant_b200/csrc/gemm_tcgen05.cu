@@ -1,0 +1,571 @@
+// Codebook-decode GEMM for large row counts on the 5th-generation tensor cores.
+//
+//   out[m, n] = (sum_k xq[m, k] * f16(centroid[idx[n, k]] * 2^8)) * row_norm[n] * 2^-8 + bias[n]
+//
+// One CTA computes a 256 x BN output tile (two 128 x BN fp32 accumulators in tensor
+// memory that share every expanded weight tile).  Warp roles:
+//
+//   warp 8 (one lane)  TMA producer: per 64-wide k step, one bulk tensor copy of the
+//                      256 x 64 bf16 activation tile (128-byte swizzle) and one of the
+//                      BN x 32-byte packed 4-bit weight tile, both signalling `full[s]`.
+//   warps 0..7         expanders: read the packed tile from shared memory, map every byte
+//                      (two indices) through a shared-memory table of half2 centroid pairs
+//                      and write the BN x 64 f16 operand tile in the 128-byte-swizzled
+//                      K-major layout the MMA descriptor expects; then `bready[s]`.
+//                      After the last k step the same warps run the epilogue.
+//   warp 9 (one lane)  MMA issuer: 2 x 4 tcgen05.mma (128 x BN x 16, bf16 x f16 -> f32)
+//                      per k step, tcgen05.commit to `empty[s]`; the last commit signals
+//                      `acc_full`.
+//   epilogue           tcgen05.ld of 32 columns at a time, scale by row_norm[n] * 2^-8,
+//                      add bias, round to bf16, 16-byte stores.
+//
+// Every mbarrier wait is bounded: when a wait gives up it raises the CTA's abort flag
+// and the device status word, every role leaves its loop, in-flight bulk copies are
+// drained (bounded again), tensor memory is released and the kernel returns.
+#include <cuda.h>
+
+#include <mutex>
+
+#include "common.cuh"
+
+namespace oq {
+
+__device__ int g_gemm_status = 0;  // 0 = ok; otherwise the code of the first wait that gave up
+
+namespace {
+
+constexpr int kBM = 256;
+constexpr int kBK = 64;
+constexpr int kLutRep = 4;
+constexpr int kThreads = 320;
+constexpr int kExpanderWarps = 8;
+constexpr int kProducerWarp = 8;
+constexpr int kMmaWarp = 9;
+constexpr float kCentroidScale = 256.0f;  // f16 operand = centroid * 2^8 (exact scaling)
+constexpr uint32_t kSpinLimit = 1u << 22;
+
+template <int BN>
+struct Tile {
+  static constexpr int kStages = BN == 256 ? 3 : 4;
+  static constexpr int kABytes = kBM * kBK * 2;        // 32 KB
+  static constexpr int kBBytes = BN * kBK * 2;         // expanded f16 tile
+  static constexpr int kPBytes = BN * (kBK / 2);       // packed 4-bit tile
+  static constexpr int kStageBytes = kABytes + kBBytes + kPBytes;
+  static constexpr int kHeaderBytes = 256 /*barriers*/ + 2 * BN * 4 /*scale,bias*/ + 256 * kLutRep * 4;
+  static constexpr int kSmemBytes = kHeaderBytes + 1024 /*alignment slack*/ + kStages * kStageBytes;
+  static constexpr int kTmemCols = 2 * BN;
+};
+
+struct GemmParams {
+  void *out;
+  const __nv_bfloat16 *row_norms;
+  const float *centroids;
+  const void *bias;
+  int bias_dtype;  // -1 none
+  int64_t rows;
+  int64_t out_features;
+  int k_iters;
+  int m_tiles;
+};
+
+// ---- PTX wrappers ------------------------------------------------------------------------
+
+__device__ __forceinline__ uint32_t smem_u32(const void *p) {
+  return static_cast<uint32_t>(__cvta_generic_to_shared(p));
+}
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
+}
+
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+
+__device__ __forceinline__ void mbar_arrive_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes)
+               : "memory");
+}
+
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+  uint32_t done;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(done)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return done != 0;
+}
+
+// Bounded wait.  Returns false (after raising the abort flag) when the barrier did not
+// flip within the spin limit or another role has already aborted.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int *abort_flag,
+                                          int code) {
+  for (uint32_t spin = 0; spin < kSpinLimit; ++spin) {
+    if (mbar_try_wait(bar, parity)) {
+      return true;
+    }
+    if ((spin & 63u) == 63u && *abort_flag != 0) {
+      return false;
+    }
+  }
+  *abort_flag = code;
+  atomicCAS(&g_gemm_status, 0, code);
+  return false;
+}
+
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap *map, uint32_t bar,
+                                            int x, int y) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+      ::"r"(dst), "l"(map), "r"(bar), "r"(x), "r"(y)
+      : "memory");
+}
+
+__device__ __forceinline__ void fence_proxy_async_smem() {
+  asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+}
+
+__device__ __forceinline__ void tc_fence_before() {
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+}
+
+__device__ __forceinline__ void tc_fence_after() {
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+}
+
+__device__ __forceinline__ void tmem_alloc(uint32_t dst_smem, uint32_t cols) {
+  asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(dst_smem),
+               "r"(cols)
+               : "memory");
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+
+__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t cols) {
+  asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(cols)
+               : "memory");
+}
+
+__device__ __forceinline__ void umma_f16(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b,
+                                         uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+
+__device__ __forceinline__ void umma_commit(uint32_t bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar)
+               : "memory");
+}
+
+__device__ __forceinline__ void tmem_ld_32x32b_x32(uint32_t taddr, uint32_t (&v)[32]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+      : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]),
+        "=r"(v[7]), "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]),
+        "=r"(v[14]), "=r"(v[15]), "=r"(v[16]), "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]),
+        "=r"(v[21]), "=r"(v[22]), "=r"(v[23]), "=r"(v[24]), "=r"(v[25]), "=r"(v[26]), "=r"(v[27]),
+        "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
+      : "r"(taddr)
+      : "memory");
+}
+
+__device__ __forceinline__ void tmem_ld_wait() {
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+
+// Shared-memory matrix descriptor of a K-major tile whose rows are 128 bytes (64 16-bit
+// values) with the 128-byte swizzle: 8-row groups are 1024 bytes apart (stride byte
+// offset), the leading byte offset is unused for this layout, descriptor version 1.
+__device__ __forceinline__ uint64_t smem_desc_k_sw128(uint32_t addr) {
+  uint64_t desc = 0;
+  desc |= static_cast<uint64_t>((addr & 0x3ffffu) >> 4);
+  desc |= static_cast<uint64_t>(1) << 16;            // leading byte offset (ignored)
+  desc |= static_cast<uint64_t>(1024 >> 4) << 32;    // stride byte offset
+  desc |= static_cast<uint64_t>(1) << 46;            // descriptor version
+  desc |= static_cast<uint64_t>(2) << 61;            // 128-byte swizzle
+  return desc;
+}
+
+// Instruction descriptor: f32 accumulator, A = bf16, B = f16, both K-major, M = 128.
+__host__ __device__ constexpr uint32_t instr_desc(int n) {
+  return (1u << 4)                             // D format f32
+         | (1u << 7)                           // A format bf16
+         | (0u << 10)                          // B format f16
+         | (static_cast<uint32_t>(n >> 3) << 17)
+         | (static_cast<uint32_t>(128 >> 4) << 24);
+}
+
+__device__ __forceinline__ float load_bias(const void *bias, int dtype, int64_t n) {
+  switch (dtype) {
+    case OQ_DTYPE_F32: return Scalar<OQ_DTYPE_F32>::load(bias, n);
+    case OQ_DTYPE_F16: return Scalar<OQ_DTYPE_F16>::load(bias, n);
+    default: return Scalar<OQ_DTYPE_BF16>::load(bias, n);
+  }
+}
+
+template <int BN>
+__global__ void __launch_bounds__(kThreads, 1)
+gemm_w4_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
+                       const __grid_constant__ CUtensorMap map_p, const GemmParams p) {
+  using T = Tile<BN>;
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  // header: barriers | scale[BN] | bias[BN] | lut[256*rep]
+  uint64_t *bars = reinterpret_cast<uint64_t *>(smem_raw);
+  uint32_t *s_tmem = reinterpret_cast<uint32_t *>(smem_raw + 192);
+  volatile int *s_abort = reinterpret_cast<volatile int *>(smem_raw + 200);
+  float *s_scale = reinterpret_cast<float *>(smem_raw + 256);
+  float *s_bias = s_scale + BN;
+  uint32_t *s_lut = reinterpret_cast<uint32_t *>(s_bias + BN);
+  const uint32_t header_end = smem_u32(smem_raw) + T::kHeaderBytes;
+  const uint32_t stage_base = (header_end + 1023u) & ~1023u;
+  unsigned char *stage_ptr = smem_raw + (stage_base - smem_u32(smem_raw));
+
+  const uint32_t bar_base = smem_u32(bars);
+  auto full_bar = [&](int s) { return bar_base + 8u * s; };
+  auto empty_bar = [&](int s) { return bar_base + 8u * (T::kStages + s); };
+  auto bready_bar = [&](int s) { return bar_base + 8u * (2 * T::kStages + s); };
+  const uint32_t acc_full_bar = bar_base + 8u * (3 * T::kStages);
+
+  auto a_addr = [&](int s) { return stage_base + s * T::kStageBytes; };
+  auto b_addr = [&](int s) { return stage_base + s * T::kStageBytes + T::kABytes; };
+  auto p_ptr = [&](int s) { return stage_ptr + s * T::kStageBytes + T::kABytes + T::kBBytes; };
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int m_tile = blockIdx.x % p.m_tiles;
+  const int n_tile = blockIdx.x / p.m_tiles;
+  const int64_t m0 = static_cast<int64_t>(m_tile) * kBM;
+  const int64_t n0 = static_cast<int64_t>(n_tile) * BN;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < T::kStages; ++s) {
+      mbar_init(full_bar(s), 1);
+      mbar_init(empty_bar(s), 1);
+      mbar_init(bready_bar(s), kExpanderWarps);
+    }
+    mbar_init(acc_full_bar, 1);
+    *s_abort = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == kMmaWarp) {
+    tmem_alloc(smem_u32(s_tmem), T::kTmemCols);
+  }
+  if (warp == kProducerWarp && lane == 0) {
+    asm volatile("prefetch.tensormap [%0];" ::"l"(&map_a) : "memory");
+    asm volatile("prefetch.tensormap [%0];" ::"l"(&map_p) : "memory");
+  }
+  // Byte -> (centroid[lo], centroid[hi]) * 2^8 as half2, replicated kLutRep times.
+  for (int v = threadIdx.x; v < 256; v += kThreads) {
+    const __half lo = __float2half_rn(p.centroids[v & 15] * kCentroidScale);
+    const __half hi = __float2half_rn(p.centroids[v >> 4] * kCentroidScale);
+    const uint32_t word = static_cast<uint32_t>(__half_as_ushort(lo)) |
+                          (static_cast<uint32_t>(__half_as_ushort(hi)) << 16);
+#pragma unroll
+    for (int c = 0; c < kLutRep; ++c) {
+      s_lut[v * kLutRep + c] = word;
+    }
+  }
+  for (int i = threadIdx.x; i < BN; i += kThreads) {
+    const int64_t n = n0 + i;
+    const bool ok = n < p.out_features;
+    s_scale[i] = ok ? __bfloat162float(p.row_norms[n]) * (1.0f / kCentroidScale) : 0.0f;
+    s_bias[i] = (ok && p.bias_dtype >= 0) ? load_bias(p.bias, p.bias_dtype, n) : 0.0f;
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *s_tmem;
+
+  if (warp == kProducerWarp) {
+    if (lane == 0) {
+      int issued = 0;
+      for (int it = 0; it < p.k_iters; ++it) {
+        const int s = it % T::kStages;
+        const uint32_t phase = (it / T::kStages) & 1u;
+        if (!mbar_wait(empty_bar(s), phase ^ 1u, s_abort, 1)) {
+          break;
+        }
+        mbar_arrive_expect_tx(full_bar(s), T::kABytes + T::kPBytes);
+        tma_load_2d(a_addr(s), &map_a, full_bar(s), it * kBK, static_cast<int>(m0));
+        tma_load_2d(smem_u32(p_ptr(s)), &map_p, full_bar(s), it * (kBK / 2), static_cast<int>(n0));
+        issued = it + 1;
+      }
+      if (*s_abort != 0) {
+        // Drain: the copies already issued must land before the CTA may exit.
+        const int first = issued > T::kStages ? issued - T::kStages : 0;
+        for (int it = first; it < issued; ++it) {
+          const uint32_t bar = full_bar(it % T::kStages);
+          const uint32_t phase = (it / T::kStages) & 1u;
+          for (uint32_t spin = 0; spin < kSpinLimit && !mbar_try_wait(bar, phase); ++spin) {
+          }
+        }
+      }
+    }
+  } else if (warp == kMmaWarp) {
+    if (lane == 0) {
+      constexpr uint32_t idesc = instr_desc(BN);
+      bool ok = true;
+      for (int it = 0; it < p.k_iters && ok; ++it) {
+        const int s = it % T::kStages;
+        const uint32_t phase = (it / T::kStages) & 1u;
+        ok = mbar_wait(full_bar(s), phase, s_abort, 2) && mbar_wait(bready_bar(s), phase, s_abort, 3);
+        if (!ok) {
+          break;
+        }
+        tc_fence_after();
+#pragma unroll
+        for (int half = 0; half < 2; ++half) {
+#pragma unroll
+          for (int j = 0; j < kBK / 16; ++j) {
+            const uint64_t da = smem_desc_k_sw128(a_addr(s) + half * (128 * 128) + j * 32);
+            const uint64_t db = smem_desc_k_sw128(b_addr(s) + j * 32);
+            umma_f16(tmem_base + half * BN, da, db, idesc, (it > 0 || j > 0) ? 1u : 0u);
+          }
+        }
+        umma_commit(empty_bar(s));
+      }
+      if (ok) {
+        umma_commit(acc_full_bar);
+      }
+    }
+  } else {
+    // ---- expanders ----
+    constexpr int kThreadsPerRow = 256 / BN;          // 1 (BN=256) or 2 (BN=128)
+    constexpr int kBytesPerThread = 32 / kThreadsPerRow;
+    constexpr int kChunksPerThread = kBytesPerThread / 4;
+    const int et = threadIdx.x;  // 0..255
+    const int row = et / kThreadsPerRow;
+    const int part = et % kThreadsPerRow;
+    const uint32_t *lut = s_lut + (lane & (kLutRep - 1));
+    const uint32_t row_off = (row >> 3) * 1024 + (row & 7) * 128;
+    bool ok = true;
+    for (int it = 0; it < p.k_iters; ++it) {
+      const int s = it % T::kStages;
+      const uint32_t phase = (it / T::kStages) & 1u;
+      if (!mbar_wait(full_bar(s), phase, s_abort, 4)) {
+        ok = false;
+        break;
+      }
+      const uint4 *src = reinterpret_cast<const uint4 *>(p_ptr(s) + row * 32 + part * kBytesPerThread);
+      uint32_t words[kChunksPerThread];
+#pragma unroll
+      for (int q = 0; q < kChunksPerThread / 4; ++q) {
+        const uint4 v = src[q];
+        words[4 * q + 0] = v.x;
+        words[4 * q + 1] = v.y;
+        words[4 * q + 2] = v.z;
+        words[4 * q + 3] = v.w;
+      }
+      const uint32_t dst_row = b_addr(s) + row_off;
+#pragma unroll
+      for (int c = 0; c < kChunksPerThread; ++c) {
+        const uint32_t w = words[c];
+        uint4 o;
+        o.x = lut[(w & 0xffu) * kLutRep];
+        o.y = lut[((w >> 8) & 0xffu) * kLutRep];
+        o.z = lut[((w >> 16) & 0xffu) * kLutRep];
+        o.w = lut[(w >> 24) * kLutRep];
+        const int chunk = part * kChunksPerThread + c;
+        const uint32_t dst = dst_row + (((chunk ^ (row & 7)) & 7) << 4);
+        asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(dst), "r"(o.x), "r"(o.y),
+                     "r"(o.z), "r"(o.w)
+                     : "memory");
+      }
+      fence_proxy_async_smem();
+      __syncwarp();
+      if (lane == 0) {
+        mbar_arrive(bready_bar(s));
+      }
+    }
+
+    // ---- epilogue: warp w reads accumulator w/4, TMEM lanes 32*(w%4).. ----
+    if (ok && mbar_wait(acc_full_bar, 0, s_abort, 5)) {
+      tc_fence_after();
+      const int half = warp >> 2;
+      const int quarter = warp & 3;
+      const int64_t m = m0 + half * 128 + quarter * 32 + lane;
+      const bool vec_ok = (p.out_features % 8) == 0;
+      __nv_bfloat16 *out_row = static_cast<__nv_bfloat16 *>(p.out) + m * p.out_features;
+#pragma unroll 1
+      for (int c0 = 0; c0 < BN; c0 += 32) {
+        uint32_t v[32];
+        tmem_ld_32x32b_x32(tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + half * BN + c0, v);
+        tmem_ld_wait();
+        if (m < p.rows) {
+          uint32_t packed[16];
+#pragma unroll
+          for (int j = 0; j < 16; ++j) {
+            const float a = fmaf(__uint_as_float(v[2 * j]), s_scale[c0 + 2 * j], s_bias[c0 + 2 * j]);
+            const float b = fmaf(__uint_as_float(v[2 * j + 1]), s_scale[c0 + 2 * j + 1], s_bias[c0 + 2 * j + 1]);
+            const __nv_bfloat162 h = __floats2bfloat162_rn(a, b);
+            packed[j] = *reinterpret_cast<const uint32_t *>(&h);
+          }
+          const int64_t n = n0 + c0;
+          if (vec_ok && n + 32 <= p.out_features) {
+            uint4 *dst = reinterpret_cast<uint4 *>(out_row + n);
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+              dst[q] = make_uint4(packed[4 * q], packed[4 * q + 1], packed[4 * q + 2], packed[4 * q + 3]);
+            }
+          } else {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) {
+              if (n + j < p.out_features) {
+                const uint16_t bits = static_cast<uint16_t>(packed[j >> 1] >> ((j & 1) * 16));
+                reinterpret_cast<uint16_t *>(out_row)[n + j] = bits;
+              }
+            }
+          }
+        }
+      }
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == kMmaWarp) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, T::kTmemCols);
+  }
+}
+
+// ---- host side ---------------------------------------------------------------------------
+
+using EncodeTiledFn = CUresult (*)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *,
+                                   const cuuint64_t *, const cuuint64_t *, const cuuint32_t *,
+                                   const cuuint32_t *, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                   CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_tiled_fn() {
+  static EncodeTiledFn fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void *ptr = nullptr;
+    cudaDriverEntryPointQueryResult result;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &result) ==
+            cudaSuccess &&
+        result == cudaDriverEntryPointSuccess) {
+      fn = reinterpret_cast<EncodeTiledFn>(ptr);
+    }
+  });
+  return fn;
+}
+
+template <int BN>
+int launch_bn(const CUtensorMap &map_a, const CUtensorMap &map_p, const GemmParams &p, int grid,
+              cudaStream_t stream) {
+  static std::once_flag once;
+  static cudaError_t attr_status = cudaSuccess;
+  std::call_once(once, [] {
+    attr_status = cudaFuncSetAttribute(gemm_w4_tcgen05_kernel<BN>,
+                                       cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                       Tile<BN>::kSmemBytes);
+  });
+  OQ_CHECK_CUDA(attr_status);
+  gemm_w4_tcgen05_kernel<BN><<<grid, kThreads, Tile<BN>::kSmemBytes, stream>>>(map_a, map_p, p);
+  OQ_CHECK_CUDA(cudaGetLastError());
+  count_launch();
+  return OQ_OK;
+}
+
+}  // namespace
+
+bool tcgen05_gemm_supported(int64_t rows, int64_t in_features, int64_t out_features, int bits,
+                            int dtype, int weight_mode) {
+  return rows > 0 && out_features > 0 && bits == 4 && dtype == OQ_DTYPE_BF16 &&
+         weight_mode != OQ_WEIGHT_BF16_SCALED && in_features >= kBK && in_features % kBK == 0 &&
+         in_features <= (1 << 30) && rows < (1ll << 31) && out_features < (1ll << 31);
+}
+
+int launch_tcgen05_gemm(void *out, const void *x, int64_t rows, int64_t in_features,
+                        int64_t out_features, const uint8_t *packed, const void *row_norms_bf16,
+                        const float *centroids, const void *bias, int bias_dtype,
+                        cudaStream_t stream) {
+  OQ_CHECK_ARG(aligned16(x) && aligned16(packed) && aligned16(out),
+               "x, packed weights and out must be 16-byte aligned for the tcgen05 kernel");
+  EncodeTiledFn encode = encode_tiled_fn();
+  if (encode == nullptr) {
+    return fail(OQ_ERR_CUDA, "cuTensorMapEncodeTiled is not available from this driver");
+  }
+  int device = 0;
+  int sm_count = 0;
+  OQ_CHECK_CUDA(cudaGetDevice(&device));
+  OQ_CHECK_CUDA(cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, device));
+
+  // Tile width: prefer 256 columns (less shared-memory traffic per flop) unless the last
+  // wave of 256-wide tiles would leave much of the machine idle and 128 fills it better.
+  const int64_t m_tiles = (rows + kBM - 1) / kBM;
+  auto wave_efficiency = [&](int bn) {
+    const int64_t tiles = m_tiles * ((out_features + bn - 1) / bn);
+    const int64_t waves = (tiles + sm_count - 1) / sm_count;
+    return static_cast<double>(tiles) / static_cast<double>(waves * sm_count);
+  };
+  const int bn = (out_features <= 128 || wave_efficiency(128) > wave_efficiency(256) + 0.08) ? 128 : 256;
+  const int64_t n_tiles = (out_features + bn - 1) / bn;
+  OQ_CHECK_ARG(m_tiles * n_tiles < (1ll << 31), "too many output tiles");
+
+  CUtensorMap map_a;
+  CUtensorMap map_p;
+  {
+    const cuuint64_t dims[2] = {static_cast<cuuint64_t>(in_features), static_cast<cuuint64_t>(rows)};
+    const cuuint64_t strides[1] = {static_cast<cuuint64_t>(in_features) * 2};
+    const cuuint32_t box[2] = {kBK, kBM};
+    const cuuint32_t elem[2] = {1, 1};
+    const CUresult rc = encode(&map_a, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void *>(x),
+                               dims, strides, box, elem, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                               CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                               CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (rc != CUDA_SUCCESS) {
+      return fail(OQ_ERR_CUDA, "cuTensorMapEncodeTiled(activations) failed with code %d", (int)rc);
+    }
+  }
+  {
+    const cuuint64_t dims[2] = {static_cast<cuuint64_t>(in_features / 2),
+                                static_cast<cuuint64_t>(out_features)};
+    const cuuint64_t strides[1] = {static_cast<cuuint64_t>(in_features / 2)};
+    const cuuint32_t box[2] = {kBK / 2, static_cast<cuuint32_t>(bn)};
+    const cuuint32_t elem[2] = {1, 1};
+    const CUresult rc = encode(&map_p, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<uint8_t *>(packed),
+                               dims, strides, box, elem, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                               CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                               CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (rc != CUDA_SUCCESS) {
+      return fail(OQ_ERR_CUDA, "cuTensorMapEncodeTiled(packed weights) failed with code %d", (int)rc);
+    }
+  }
+
+  GemmParams p{};
+  p.out = out;
+  p.row_norms = static_cast<const __nv_bfloat16 *>(row_norms_bf16);
+  p.centroids = centroids;
+  p.bias = bias;
+  p.bias_dtype = bias == nullptr ? -1 : bias_dtype;
+  p.rows = rows;
+  p.out_features = out_features;
+  p.k_iters = static_cast<int>(in_features / kBK);
+  p.m_tiles = static_cast<int>(m_tiles);
+  const int grid = static_cast<int>(m_tiles * n_tiles);
+  return bn == 256 ? launch_bn<256>(map_a, map_p, p, grid, stream)
+                   : launch_bn<128>(map_a, map_p, p, grid, stream);
+}
+
+int read_gemm_status(int *status) {
+  OQ_CHECK_CUDA(cudaMemcpyFromSymbol(status, g_gemm_status, sizeof(int)));
+  return OQ_OK;
+}
+
+int clear_gemm_status() {
+  const int zero = 0;
+  OQ_CHECK_CUDA(cudaMemcpyToSymbol(g_gemm_status, &zero, sizeof(int)));
+  return OQ_OK;
+}
+
+}  // namespace oq

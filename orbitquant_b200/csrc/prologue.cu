@@ -1,0 +1,399 @@
+// Fused RPBH rotate-and-quantize prologue (online activation quantisation).
+//
+// One CTA owns `rows_per_cta` tokens at a time and keeps them in shared memory from the
+// first load to the last store, so a token is read from HBM once and written once:
+//
+//   1. the raw rows arrive by 16-byte vector loads;
+//   2. per-token sum of squares in the reference's AVX-512 order: 16 fused-multiply-add
+//      lanes striding the row, folded 8/4/2/1 by xor-shuffles (commutative adds, so the
+//      tree equals _mm512_reduce_add_ps);
+//   3. each warp takes 256-element chunks: lane l gathers x[perm[i]]*sign[i]*(1/(n+eps))
+//      for its 8 consecutive i, runs butterfly widths 1,2,4 in registers and 8..128 as
+//      warp-shuffle butterflies -- a complete 256-point Walsh-Hadamard per warp;
+//   4. blocks wider than 256 finish in a second pass where one thread owns the
+//      block/256 values 256 apart and runs the remaining widths 256,512,... in registers;
+//   5. branch-free bucketize against the Lloyd-Max boundaries, centroid*norm, round to the
+//      activation dtype, and the row leaves by 16-byte vector stores.
+//
+// Butterfly widths run in increasing order and every pair computes (l + r, l - r) with l
+// the lower index, which keeps the fp32 result bit-identical to the reference's kernels.
+#include "common.cuh"
+
+namespace oq {
+namespace {
+
+constexpr int kThreads = 256;
+constexpr int kWarps = kThreads / 32;
+constexpr int kChunk = 256;  // elements one warp transforms at a time (8 per lane)
+
+struct PrologueParams {
+  const void *x;
+  void *xq;
+  uint8_t *codes;
+  float *norms;
+  const int32_t *perm;
+  const int8_t *signs;
+  const float *boundaries;
+  const float *centroids;
+  int64_t rows;
+  int dim;
+  int block;
+  int bits;
+  int rows_per_cta;
+  float eps;
+  float inv_sqrt_block;
+};
+
+// Number of boundaries strictly below `v` (sorted ascending, count = 2^bits - 1), as a
+// branch-free binary search.  `!(v <= b)` keeps the reference's treatment of NaN (counts
+// as above every boundary).
+__device__ __forceinline__ int bucketize(float v, const float *bnd, int bits) {
+  int pos = 0;
+#pragma unroll 1
+  for (int step = 1 << (bits - 1); step >= 1; step >>= 1) {
+    pos += !(v <= bnd[pos + step - 1]) ? step : 0;
+  }
+  return pos;
+}
+
+template <int DTYPE>
+__device__ __forceinline__ void emit(const PrologueParams &p, void *stage, const float *s_bnd,
+                                     const float *s_cent, int64_t row, int r, int i, float v,
+                                     float norm) {
+  const float direction = __fmul_rn(v, p.inv_sqrt_block);
+  const int idx = bucketize(direction, s_bnd, p.bits);
+  const float q = __fmul_rn(s_cent[idx], norm);
+  Scalar<DTYPE>::store(stage, static_cast<int64_t>(r) * p.dim + i, q);
+  if (p.codes != nullptr) {
+    p.codes[row * p.dim + i] = static_cast<uint8_t>(idx);
+  }
+}
+
+// Remaining butterfly widths 256, 512, ... for one group of S values 256 apart.
+template <int S>
+__device__ __forceinline__ void strided_butterflies(float (&v)[S]) {
+#pragma unroll
+  for (int h = 1; h < S; h <<= 1) {
+#pragma unroll
+    for (int a = 0; a < S; ++a) {
+      if ((a & h) == 0) {
+        const float l = v[a];
+        const float r = v[a | h];
+        v[a] = __fadd_rn(l, r);
+        v[a | h] = __fsub_rn(l, r);
+      }
+    }
+  }
+}
+
+template <int DTYPE, int S>
+__device__ __forceinline__ void second_pass(const PrologueParams &p, float *rot, void *stage,
+                                            const float *s_bnd, const float *s_cent,
+                                            const float *s_norm, int64_t row_base, int nrows) {
+  // group g of a row: block b = g / 256, column j = g % 256; values at b*block + j + 256*s.
+  const int groups_per_row = p.dim / S;
+  const int total = groups_per_row * nrows;
+  for (int item = threadIdx.x; item < total; item += kThreads) {
+    const int r = item / groups_per_row;
+    const int g = item - r * groups_per_row;
+    const int base = (g / kChunk) * p.block + (g % kChunk);
+    float *src = rot + static_cast<int64_t>(r) * p.dim + base;
+    float v[S];
+#pragma unroll
+    for (int s = 0; s < S; ++s) {
+      v[s] = src[s * kChunk];
+    }
+    strided_butterflies<S>(v);
+    const float norm = s_norm[r];
+#pragma unroll
+    for (int s = 0; s < S; ++s) {
+      emit<DTYPE>(p, stage, s_bnd, s_cent, row_base + r, r, base + s * kChunk, v[s], norm);
+    }
+  }
+}
+
+template <int DTYPE>
+__global__ void __launch_bounds__(kThreads)
+rotate_quantize_kernel(const PrologueParams p) {
+  using elem_t = typename Scalar<DTYPE>::type;
+  extern __shared__ __align__(16) unsigned char smem[];
+  const int dim = p.dim;
+  const int R = p.rows_per_cta;
+  float *rot = reinterpret_cast<float *>(smem);                       // [R][dim] fp32
+  elem_t *xin = reinterpret_cast<elem_t *>(rot + static_cast<size_t>(R) * dim);  // [R][dim]
+  float *s_bnd = reinterpret_cast<float *>(xin + static_cast<size_t>(R) * dim);
+  float *s_cent = s_bnd + 256;
+  float *s_norm = s_cent + 256;  // [R] norms
+  float *s_inv = s_norm + 8;     // [R] 1/(norm+eps)
+
+  const int levels = 1 << p.bits;
+  for (int i = threadIdx.x; i < levels; i += kThreads) {
+    s_cent[i] = p.centroids[i];
+    if (i < levels - 1) {
+      s_bnd[i] = p.boundaries[i];
+    }
+  }
+
+  const int lane = threadIdx.x & 31;
+  const int warp = threadIdx.x >> 5;
+  const bool wide = p.block > kChunk;
+  // Quantised rows are staged in whichever buffer is idle while they are produced.
+  void *stage = wide ? static_cast<void *>(xin) : static_cast<void *>(rot);
+  const int chunks = (dim + kChunk - 1) / kChunk;
+  constexpr int kVec = 16 / static_cast<int>(sizeof(elem_t));
+  const bool vec_ok = (dim % kVec) == 0;
+
+  for (int64_t row_base = static_cast<int64_t>(blockIdx.x) * R; row_base < p.rows;
+       row_base += static_cast<int64_t>(gridDim.x) * R) {
+    const int nrows = static_cast<int>(min(static_cast<int64_t>(R), p.rows - row_base));
+    __syncthreads();  // previous iteration's stores are done with the staging buffer
+
+    // 1. load
+    const elem_t *src = static_cast<const elem_t *>(p.x) + row_base * dim;
+    const int total = nrows * dim;
+    if (vec_ok) {
+      const uint4 *src4 = reinterpret_cast<const uint4 *>(src);
+      uint4 *dst4 = reinterpret_cast<uint4 *>(xin);
+      for (int i = threadIdx.x; i < total / kVec; i += kThreads) {
+        dst4[i] = __ldg(src4 + i);
+      }
+    } else {
+      for (int i = threadIdx.x; i < total; i += kThreads) {
+        xin[i] = src[i];
+      }
+    }
+    __syncthreads();
+
+    // 2. norms: thread t -> row t/16, lane-of-16 t%16
+    if (threadIdx.x < ((16 * nrows + 31) & ~31)) {
+      const int r = threadIdx.x >> 4;
+      const int j = threadIdx.x & 15;
+      float acc = 0.0f;
+      if (r < nrows) {
+        const elem_t *xr = xin + static_cast<size_t>(r) * dim;
+        const int full = dim & ~15;
+        for (int i = j; i < full; i += 16) {
+          const float v = static_cast<float>(xr[i]);
+          acc = __fmaf_rn(v, v, acc);
+        }
+      }
+      acc = __fadd_rn(acc, __shfl_xor_sync(0xffffffffu, acc, 8));
+      acc = __fadd_rn(acc, __shfl_xor_sync(0xffffffffu, acc, 4));
+      acc = __fadd_rn(acc, __shfl_xor_sync(0xffffffffu, acc, 2));
+      acc = __fadd_rn(acc, __shfl_xor_sync(0xffffffffu, acc, 1));
+      if (r < nrows && j == 0) {
+        const elem_t *xr = xin + static_cast<size_t>(r) * dim;
+        for (int i = dim & ~15; i < dim; ++i) {
+          const float v = static_cast<float>(xr[i]);
+          acc = __fadd_rn(acc, __fmul_rn(v, v));
+        }
+        const float norm = __fsqrt_rn(acc);
+        s_norm[r] = norm;
+        s_inv[r] = __fdiv_rn(1.0f, __fadd_rn(norm, p.eps));
+        if (p.norms != nullptr) {
+          p.norms[row_base + r] = norm;
+        }
+      }
+    }
+    __syncthreads();
+
+    // 3. gather + 256-point transform per (row, chunk)
+    const int items = nrows * chunks;
+    for (int item = warp; item < items; item += kWarps) {
+      const int r = item / chunks;
+      const int c = item - r * chunks;
+      const int i0 = c * kChunk + lane * 8;
+      const elem_t *xr = xin + static_cast<size_t>(r) * dim;
+      const float inv = s_inv[r];
+      float v[8];
+      if (i0 + 8 <= dim) {
+        const int4 pa = __ldg(reinterpret_cast<const int4 *>(p.perm + i0));
+        const int4 pb = __ldg(reinterpret_cast<const int4 *>(p.perm + i0 + 4));
+        const int2 sg = __ldg(reinterpret_cast<const int2 *>(p.signs + i0));
+        const int pi[8] = {pa.x, pa.y, pa.z, pa.w, pb.x, pb.y, pb.z, pb.w};
+#pragma unroll
+        for (int e = 0; e < 8; ++e) {
+          const int sbyte = ((e < 4 ? sg.x : sg.y) >> (8 * (e & 3))) & 0xff;
+          const float sign = static_cast<float>(static_cast<signed char>(sbyte));
+          v[e] = __fmul_rn(__fmul_rn(static_cast<float>(xr[pi[e]]), sign), inv);
+        }
+      } else {
+#pragma unroll
+        for (int e = 0; e < 8; ++e) {
+          const int i = i0 + e;
+          v[e] = 0.0f;
+          if (i < dim) {
+            const float sign = static_cast<float>(p.signs[i]);
+            v[e] = __fmul_rn(__fmul_rn(static_cast<float>(xr[p.perm[i]]), sign), inv);
+          }
+        }
+      }
+      // widths 1, 2, 4 in registers
+#pragma unroll
+      for (int h = 1; h < 8; h <<= 1) {
+        if (h < p.block) {
+#pragma unroll
+          for (int a = 0; a < 8; ++a) {
+            if ((a & h) == 0) {
+              const float l = v[a];
+              const float rr = v[a | h];
+              v[a] = __fadd_rn(l, rr);
+              v[a | h] = __fsub_rn(l, rr);
+            }
+          }
+        }
+      }
+      // widths 8 .. 128 across lanes
+#pragma unroll
+      for (int m = 1; m < 32; m <<= 1) {
+        if (m * 8 < p.block) {
+          const bool upper = (lane & m) != 0;
+#pragma unroll
+          for (int e = 0; e < 8; ++e) {
+            const float other = __shfl_xor_sync(0xffffffffu, v[e], m);
+            v[e] = upper ? __fsub_rn(other, v[e]) : __fadd_rn(v[e], other);
+          }
+        }
+      }
+      if (wide) {
+        if (i0 + 8 <= dim) {
+          float4 *dst = reinterpret_cast<float4 *>(rot + static_cast<size_t>(r) * dim + i0);
+          dst[0] = make_float4(v[0], v[1], v[2], v[3]);
+          dst[1] = make_float4(v[4], v[5], v[6], v[7]);
+        }
+      } else {
+        const float norm = s_norm[r];
+#pragma unroll
+        for (int e = 0; e < 8; ++e) {
+          if (i0 + e < dim) {
+            emit<DTYPE>(p, stage, s_bnd, s_cent, row_base + r, r, i0 + e, v[e], norm);
+          }
+        }
+      }
+    }
+    __syncthreads();
+
+    // 4. widths >= 256
+    if (wide) {
+      switch (p.block / kChunk) {
+        case 2: second_pass<DTYPE, 2>(p, rot, stage, s_bnd, s_cent, s_norm, row_base, nrows); break;
+        case 4: second_pass<DTYPE, 4>(p, rot, stage, s_bnd, s_cent, s_norm, row_base, nrows); break;
+        case 8: second_pass<DTYPE, 8>(p, rot, stage, s_bnd, s_cent, s_norm, row_base, nrows); break;
+        case 16: second_pass<DTYPE, 16>(p, rot, stage, s_bnd, s_cent, s_norm, row_base, nrows); break;
+        case 32: second_pass<DTYPE, 32>(p, rot, stage, s_bnd, s_cent, s_norm, row_base, nrows); break;
+        default: second_pass<DTYPE, 64>(p, rot, stage, s_bnd, s_cent, s_norm, row_base, nrows); break;
+      }
+      __syncthreads();
+    }
+
+    // 5. store
+    if (p.xq != nullptr) {
+      elem_t *dst = static_cast<elem_t *>(p.xq) + row_base * dim;
+      if (vec_ok) {
+        const uint4 *s4 = reinterpret_cast<const uint4 *>(stage);
+        uint4 *d4 = reinterpret_cast<uint4 *>(dst);
+        for (int i = threadIdx.x; i < total / kVec; i += kThreads) {
+          d4[i] = s4[i];
+        }
+      } else {
+        const elem_t *s = static_cast<const elem_t *>(stage);
+        for (int i = threadIdx.x; i < total; i += kThreads) {
+          dst[i] = s[i];
+        }
+      }
+    }
+  }
+}
+
+size_t prologue_smem_bytes(int dim, int rows_per_cta, int dtype) {
+  return static_cast<size_t>(rows_per_cta) * dim * (4 + dtype_size(dtype)) + (256 + 256 + 16) * 4;
+}
+
+}  // namespace
+
+// Largest block the two-pass scheme covers: 256 (warp) x 64 (registers).
+constexpr int64_t kMaxBlock = 256 * 64;
+
+int launch_rotate_quantize(const void *x, int x_dtype, int64_t rows, int64_t dim,
+                           const int32_t *perm, const int8_t *signs, int64_t block,
+                           const float *boundaries, const float *centroids, int bits, float eps,
+                           void *x_q, uint8_t *codes, float *norms, cudaStream_t stream) {
+  OQ_CHECK_ARG(valid_dtype(x_dtype), "x must be float32, float16, or bfloat16");
+  OQ_CHECK_ARG(rows >= 0 && dim > 0, "rows must be >= 0 and dim positive");
+  OQ_CHECK_ARG(block > 0 && (block & (block - 1)) == 0, "block_size must be a positive power of two");
+  OQ_CHECK_ARG(dim % block == 0, "block_size must divide the input dimension");
+  OQ_CHECK_ARG(block <= kMaxBlock, "block_size above %lld is not supported", (long long)kMaxBlock);
+  OQ_CHECK_ARG(bits >= 1 && bits <= 8, "bits must be in [1, 8]");
+  OQ_CHECK_ARG(eps >= 0.0f, "eps must be non-negative");
+  OQ_CHECK_ARG(dim <= (1 << 20), "dim above 2^20 is not supported");
+  OQ_CHECK_ARG(x != nullptr && perm != nullptr && signs != nullptr && boundaries != nullptr &&
+                   centroids != nullptr, "null device pointer");
+  if (rows == 0) {
+    return OQ_OK;
+  }
+  OQ_CHECK_ARG(aligned16(x) && (x_q == nullptr || aligned16(x_q)) && aligned16(perm) &&
+                   (reinterpret_cast<uintptr_t>(signs) & 7u) == 0,
+               "x, x_q and perm must be 16-byte aligned, signs 8-byte aligned");
+
+  int device = 0;
+  OQ_CHECK_CUDA(cudaGetDevice(&device));
+  int sm_count = 0;
+  int max_smem = 0;
+  OQ_CHECK_CUDA(cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, device));
+  OQ_CHECK_CUDA(cudaDeviceGetAttribute(&max_smem, cudaDevAttrMaxSharedMemoryPerBlockOptin, device));
+
+  // Rows per CTA: enough (row, chunk) items to fill the 8 warps evenly, within ~96 KB so
+  // two CTAs share an SM, and never more than the problem offers per SM.
+  const int chunks = static_cast<int>((dim + kChunk - 1) / kChunk);
+  int rows_per_cta = 1;
+  for (int r = 1; r <= 8; r *= 2) {
+    if (prologue_smem_bytes(static_cast<int>(dim), r, x_dtype) > 96 * 1024 ||
+        static_cast<int64_t>(r) * sm_count > rows) {
+      break;
+    }
+    rows_per_cta = r;
+    if ((r * chunks) % kWarps == 0) {
+      break;
+    }
+  }
+  const size_t smem = prologue_smem_bytes(static_cast<int>(dim), rows_per_cta, x_dtype);
+  OQ_CHECK_ARG(smem <= static_cast<size_t>(max_smem),
+               "dim %lld needs %zu bytes of shared memory per token (limit %d)", (long long)dim,
+               smem, max_smem);
+
+  PrologueParams p{};
+  p.x = x;
+  p.xq = x_q;
+  p.codes = codes;
+  p.norms = norms;
+  p.perm = perm;
+  p.signs = signs;
+  p.boundaries = boundaries;
+  p.centroids = centroids;
+  p.rows = rows;
+  p.dim = static_cast<int>(dim);
+  p.block = static_cast<int>(block);
+  p.bits = bits;
+  p.rows_per_cta = rows_per_cta;
+  p.eps = eps;
+  p.inv_sqrt_block = static_cast<float>(1.0 / sqrt(static_cast<double>(block)));
+
+  const int64_t ctas_needed = (rows + rows_per_cta - 1) / rows_per_cta;
+  const int grid = static_cast<int>(std::min<int64_t>(ctas_needed, static_cast<int64_t>(sm_count) * 8));
+  void (*kernel)(PrologueParams) = nullptr;
+  switch (x_dtype) {
+    case OQ_DTYPE_F32: kernel = rotate_quantize_kernel<OQ_DTYPE_F32>; break;
+    case OQ_DTYPE_F16: kernel = rotate_quantize_kernel<OQ_DTYPE_F16>; break;
+    default: kernel = rotate_quantize_kernel<OQ_DTYPE_BF16>; break;
+  }
+  if (smem > 48 * 1024) {
+    OQ_CHECK_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                       static_cast<int>(smem)));
+  }
+  kernel<<<grid, kThreads, smem, stream>>>(p);
+  OQ_CHECK_CUDA(cudaGetLastError());
+  count_launch();
+  return OQ_OK;
+}
+
+}  // namespace oq

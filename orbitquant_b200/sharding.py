@@ -1,0 +1,91 @@
+"""Output-feature (N) sharding of an ``OrbitQuantLinear`` across the GPUs of one box.
+
+Every output column of ``y = x_q W^T + b`` depends on one packed weight row, one row norm,
+one bias element and the WHOLE quantised activation row; the token norm and the global
+RPBH permutation span all of K.  So the path shards along N and only along N: rank r keeps
+a contiguous run of rows of the row-major bit stream (a contiguous byte range because
+``K*bits`` is a multiple of 8), the matching ``row_norms`` / ``bias`` slices, and replicates
+the (cheap) rotate-and-quantize prologue.  No collective is needed to compute a shard; an
+all-gather of the ``[M, N/R]`` slices runs only when the consumer needs full rows
+(``gather_columns``).  The reference has no multi-GPU code; this module has no counterpart
+there.
+"""
+from __future__ import annotations
+
+import torch
+import torch.distributed as dist
+
+from .config import OrbitQuantConfig
+from .layers import OrbitQuantLinear
+
+# Shard boundaries fall on multiples of this many rows, so every shard's byte offset is
+# 16-byte aligned for any K*bits that is a multiple of 16 (TMA and vector loads need it).
+ROW_ALIGN = 8
+
+
+def shard_bounds(out_features: int, world_size: int, rank: int, align: int = ROW_ALIGN):
+    """Contiguous ``[lo, hi)`` rows of rank ``rank``; sizes differ by at most ``align``."""
+    if world_size <= 0 or not 0 <= rank < world_size:
+        raise ValueError("rank must be in [0, world_size)")
+    units = (out_features + align - 1) // align
+    base, extra = divmod(units, world_size)
+    lo_units = rank * base + min(rank, extra)
+    hi_units = lo_units + base + (1 if rank < extra else 0)
+    return min(lo_units * align, out_features), min(hi_units * align, out_features)
+
+
+def shard_byte_range(lo: int, hi: int, in_features: int, bits: int):
+    if (in_features * bits) % 8 != 0:
+        raise ValueError("rows must end on byte boundaries to shard the packed stream "
+                         "(in_features * bits must be a multiple of 8)")
+    row_bytes = in_features * bits // 8
+    return lo * row_bytes, hi * row_bytes
+
+
+def shard_linear(module: OrbitQuantLinear, rank: int, world_size: int,
+                 config: OrbitQuantConfig | None = None) -> OrbitQuantLinear:
+    """The rank's column shard as a stand-alone ``OrbitQuantLinear`` (views, no copies)."""
+    lo, hi = shard_bounds(module.out_features, world_size, rank)
+    b0, b1 = shard_byte_range(lo, hi, module.in_features, module.weight_bits)
+    if config is None:
+        config = OrbitQuantConfig(
+            weight_bits=module.weight_bits, activation_bits=module.activation_bits,
+            rotation_seed=module.rotation.seed, block_size=module.rotation.block_size,
+            activation_eps=module.activation_eps,
+            codebook_version=module.weight_codebook.algorithm_version)
+    shard = OrbitQuantLinear(
+        in_features=module.in_features, out_features=hi - lo, config=config,
+        module_name=f"{module.module_name}[{lo}:{hi}]",
+        source_weight_layout=module.source_weight_layout,
+        bias=None if module.bias is None else module.bias.detach()[lo:hi],
+        packed_weight_indices=module.packed_weight_indices.detach()[b0:b1],
+        row_norms=module.row_norms.detach()[lo:hi], debug_weight=None)
+    shard.weight_mode = module.weight_mode
+    shard.kernel = module.kernel
+    shard.shard_rows = (lo, hi)
+    return shard
+
+
+def gather_columns(y_local: torch.Tensor, out_features: int, group=None) -> torch.Tensor:
+    """All-gather ``[..., n_r]`` column slices (rank order) into ``[..., out_features]``.
+
+    Shards may be ragged (``shard_bounds``); slices are padded to the widest shard for the
+    collective and trimmed afterwards.  One ``all_gather`` over NCCL (NVLink/NVSwitch) on
+    GPUs, gloo on CPU."""
+    world = dist.get_world_size(group)
+    if world == 1:
+        return y_local
+    widths = [hi - lo for lo, hi in (shard_bounds(out_features, world, r) for r in range(world))]
+    widest = max(widths)
+    lead = y_local.shape[:-1]
+    flat = y_local.reshape(-1, y_local.shape[-1])
+    if flat.shape[-1] != widest:
+        flat = torch.nn.functional.pad(flat, (0, widest - flat.shape[-1]))
+    flat = flat.contiguous()
+    gathered = torch.empty((world, flat.shape[0], widest), dtype=flat.dtype, device=flat.device)
+    dist.all_gather_into_tensor(gathered, flat, group=group)
+    if all(w == widest for w in widths):
+        full = gathered.permute(1, 0, 2).reshape(flat.shape[0], world * widest)
+    else:
+        full = torch.cat([gathered[r, :, :widths[r]] for r in range(world)], dim=-1)
+    return full.reshape(*lead, out_features)
