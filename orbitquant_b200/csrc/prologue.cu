@@ -121,7 +121,9 @@ rotate_quantize_kernel(const PrologueParams p) {
   const int R = p.rows_per_cta;
   float *rot = reinterpret_cast<float *>(smem);                       // [R][dim] fp32
   elem_t *xin = reinterpret_cast<elem_t *>(rot + static_cast<size_t>(R) * dim);  // [R][dim]
-  float *s_bnd = reinterpret_cast<float *>(xin + static_cast<size_t>(R) * dim);
+  const size_t tables_offset =
+      (static_cast<size_t>(R) * dim * (sizeof(float) + sizeof(elem_t)) + 15) & ~static_cast<size_t>(15);
+  float *s_bnd = reinterpret_cast<float *>(smem + tables_offset);
   float *s_cent = s_bnd + 256;
   float *s_norm = s_cent + 256;  // [R] norms
   float *s_inv = s_norm + 8;     // [R] 1/(norm+eps)
@@ -306,7 +308,8 @@ rotate_quantize_kernel(const PrologueParams p) {
 }
 
 size_t prologue_smem_bytes(int dim, int rows_per_cta, int dtype) {
-  return static_cast<size_t>(rows_per_cta) * dim * (4 + dtype_size(dtype)) + (256 + 256 + 16) * 4;
+  return ((static_cast<size_t>(rows_per_cta) * dim * (4 + dtype_size(dtype)) + 15) & ~static_cast<size_t>(15)) +
+         (256 + 256 + 16) * 4;
 }
 
 }  // namespace

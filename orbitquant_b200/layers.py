@@ -34,11 +34,12 @@ from .config import OrbitQuantConfig
 from .packing import pack_lowbit, packed_length
 from .rotations import RPBHRotation, get_rpbh_rotation
 
-_COMPILE_REGISTRY: dict[int, object] = {}
+_COMPILE_REGISTRY: dict[int, "weakref.ref"] = {}
 
 
 def _registry_lookup(handle: int):
-    module = _COMPILE_REGISTRY.get(handle)
+    ref = _COMPILE_REGISTRY.get(handle)
+    module = None if ref is None else ref()
     if module is None:
         raise RuntimeError(
             "orbitquant compiled-forward handle is stale; rebuild the module before calling "
@@ -49,7 +50,9 @@ def _registry_lookup(handle: int):
 def _registry_register(module) -> int:
     handle = id(module)
     if handle not in _COMPILE_REGISTRY:
-        _COMPILE_REGISTRY[handle] = module
+        # A weak reference: the registry must not keep a replaced module (and its packed
+        # weights) alive; the finalizer drops the entry when the module dies.
+        _COMPILE_REGISTRY[handle] = weakref.ref(module)
         weakref.finalize(module, _COMPILE_REGISTRY.pop, handle, None)
     return handle
 
@@ -251,9 +254,13 @@ class OrbitQuantLinear(nn.Module):
             setattr(self, name, source.to(device=device, dtype=dtype).clone())
         self._derived_constants_valid = True
 
-    def _bias_for(self, device: torch.device, dtype: torch.dtype) -> torch.Tensor | None:
+    def _bias_for(self, device: torch.device) -> torch.Tensor | None:
+        """The bias in its own floating dtype: the kernels add it in fp32 before the final
+        cast (as the reference's CPU kernels do with their fp32 bias), so nothing is gained
+        by rounding it to the activation dtype first."""
         if self.bias is None:
             return None
+        dtype = self.bias.dtype if self.bias.dtype in native.DTYPE_CODES else torch.float32
         if self.bias.device == device and self.bias.dtype == dtype and self.bias.is_contiguous():
             return self.bias
         key = (str(device), dtype)
@@ -297,7 +304,7 @@ class OrbitQuantLinear(nn.Module):
         self.last_activation_kernel_backend = "orbit_b200"
         self.last_forward_device_type = "cuda"
         return native.linear_forward(
-            x, packed, self._row_norms_for(device), self._bias_for(device, x.dtype),
+            x, packed, self._row_norms_for(device), self._bias_for(device),
             permutation=self._rotation_permutation, signs=self._rotation_signs,
             block_size=self.rotation.block_size,
             act_boundaries=self._activation_codebook_boundaries,

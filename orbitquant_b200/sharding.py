@@ -82,8 +82,10 @@ def gather_columns(y_local: torch.Tensor, out_features: int, group=None) -> torc
     if flat.shape[-1] != widest:
         flat = torch.nn.functional.pad(flat, (0, widest - flat.shape[-1]))
     flat = flat.contiguous()
-    gathered = torch.empty((world, flat.shape[0], widest), dtype=flat.dtype, device=flat.device)
-    dist.all_gather_into_tensor(gathered, flat, group=group)
+    # The collective concatenates along dim 0 (gloo accepts only that shape).
+    stacked = torch.empty((world * flat.shape[0], widest), dtype=flat.dtype, device=flat.device)
+    dist.all_gather_into_tensor(stacked, flat, group=group)
+    gathered = stacked.view(world, flat.shape[0], widest)
     if all(w == widest for w in widths):
         full = gathered.permute(1, 0, 2).reshape(flat.shape[0], world * widest)
     else:

@@ -29,12 +29,20 @@ def test_codebook_bit_equal_to_reference(golden_codebooks, dim, bits):
 
 
 def test_codebook_reference_known_answer():
-    # The reference's own known-answer test (tests/test_codebooks.py:33-62): dim 32, 3 bits.
+    # The reference's own known-answer vectors (tests/test_codebooks.py:33-62, :82-102):
+    # dim 32, 3 bits, algorithm versions 2 and 1, tolerance 1e-6.
     cb = get_codebook(32, 3, 2)
-    expected = torch.tensor([-0.3662684, -0.2324367, -0.1317560, -0.0428515,
-                             0.0428515, 0.1317560, 0.2324367, 0.3662684])
-    assert torch.allclose(cb.centroids, expected, atol=1e-6)
-    assert torch.allclose(cb.boundaries, (expected[:-1] + expected[1:]) / 2, atol=1e-6)
+    expected = torch.tensor([-0.36626825, -0.23246057, -0.13175610, -0.04285152,
+                             0.04285152, 0.13175610, 0.23246057, 0.36626825])
+    bounds = torch.tensor([-0.29936442, -0.18210834, -0.08730381, 0.0,
+                           0.08730381, 0.18210834, 0.29936442])
+    torch.testing.assert_close(cb.centroids, expected, atol=1e-6, rtol=0)
+    torch.testing.assert_close(cb.boundaries, bounds, atol=1e-6, rtol=0)
+    legacy = get_codebook(32, 3, 1)
+    expected_v1 = torch.tensor([-0.36600566, -0.23213057, -0.13146324, -0.04273151,
+                                0.04273151, 0.13146324, 0.23213057, 0.36600566])
+    assert legacy.algorithm_version == 1
+    torch.testing.assert_close(legacy.centroids, expected_v1, atol=1e-6, rtol=0)
 
 
 def test_codebook_symmetry_and_order():

@@ -45,7 +45,8 @@ def test_shard_linear_views_the_byte_stream():
     assert torch.equal(torch.cat([p.row_norms for p in parts]), full.row_norms)
     assert torch.equal(torch.cat([p.bias for p in parts]), full.bias)
     assert parts[1].shard_rows == shard_bounds(40, 3, 1)
-    assert parts[0].rotation is full.rotation
+    assert torch.equal(parts[0].rotation.permutation, full.rotation.permutation)
+    assert parts[0].rotation.block_size == full.rotation.block_size
 
 
 def _worker(rank: int, world: int, port: int, out_path: str):
