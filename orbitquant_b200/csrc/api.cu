@@ -19,7 +19,8 @@ int fail(int status, const char *format, ...) {
 int launch_rotate_quantize(const void *x, int x_dtype, int64_t rows, int64_t dim,
                            const int32_t *perm, const int8_t *signs, int64_t block,
                            const float *boundaries, const float *centroids, int bits, float eps,
-                           void *x_q, uint8_t *codes, float *norms, cudaStream_t stream);
+                           void *x_q, uint8_t *codes, float *norms, float *f16_row_scale,
+                           cudaStream_t stream);
 int launch_tiled_matmul(void *out, const void *x, int dtype, int64_t rows, int64_t in_features,
                         int64_t out_features, const uint8_t *packed, int bits,
                         const void *row_norms_bf16, const float *centroids, const void *bias,
@@ -39,10 +40,12 @@ int launch_dequantize(const uint8_t *packed, int bits, int64_t out_features, int
                       int out_dtype, cudaStream_t stream);
 bool tcgen05_gemm_supported(int64_t rows, int64_t in_features, int64_t out_features, int bits,
                             int dtype, int weight_mode);
-int launch_tcgen05_gemm(void *out, const void *x, int64_t rows, int64_t in_features,
-                        int64_t out_features, const uint8_t *packed, const void *row_norms_bf16,
-                        const float *centroids, const void *bias, int bias_dtype,
-                        cudaStream_t stream);
+int launch_rows_to_f16(const void *x, int dtype, int64_t rows, int64_t dim, void *out_f16,
+                       float *row_scale, cudaStream_t stream);
+int launch_tcgen05_gemm(void *out, const void *x_f16, const float *row_scale, int64_t rows,
+                        int64_t in_features, int64_t out_features, const uint8_t *packed,
+                        const void *row_norms_bf16, const float *centroids, const void *bias,
+                        int bias_dtype, cudaStream_t stream);
 int read_gemm_status(int *status);
 int clear_gemm_status();
 
@@ -72,6 +75,26 @@ int resolve_weight_mode(int weight_mode) {
 }
 
 size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
+
+// Kernel for a problem: the caller's explicit choice, or by shape.
+int choose_kernel(int kernel, int64_t rows, int64_t in_features, int64_t out_features, int bits,
+                  int dtype, int mode) {
+  if (kernel != OQ_KERNEL_AUTO) {
+    return kernel;
+  }
+  if (rows <= 16 && small_rows_supported(rows, in_features, out_features, bits, dtype, mode)) {
+    return OQ_KERNEL_SMALL_ROWS;
+  }
+  if (rows > 16 && tcgen05_gemm_supported(rows, in_features, out_features, bits, dtype, mode)) {
+    return OQ_KERNEL_TCGEN05;
+  }
+  return OQ_KERNEL_TILED;
+}
+
+// Bytes of the f16 operand [rows, K] (256-aligned); the per-token factors follow it.
+size_t f16_operand_bytes(int64_t rows, int64_t in_features) {
+  return align_up(static_cast<size_t>(rows) * in_features * 2, 256);
+}
 
 }  // namespace
 }  // namespace oq
@@ -137,7 +160,7 @@ int oq_quantize_activations(const void *x, int x_dtype, int64_t rows, int64_t di
     return rc;
   }
   return launch_rotate_quantize(x, x_dtype, rows, dim, perm, signs, block, boundaries, centroids,
-                                bits, eps, x_q, codes, norms, static_cast<cudaStream_t>(stream));
+                                bits, eps, x_q, codes, norms, nullptr, static_cast<cudaStream_t>(stream));
 }
 
 int oq_gemm_tcgen05_supported(int64_t rows, int64_t in_features, int64_t out_features, int bits,
@@ -148,15 +171,23 @@ int oq_gemm_tcgen05_supported(int64_t rows, int64_t in_features, int64_t out_fea
              : 0;
 }
 
-size_t oq_matmul_workspace_bytes(int64_t, int64_t, int64_t, int, int, int, int) { return 0; }
+size_t oq_matmul_workspace_bytes(int64_t rows, int64_t in_features, int64_t out_features, int bits,
+                                 int dtype, int weight_mode, int kernel) {
+  if (rows <= 0 || in_features <= 0 || out_features <= 0) {
+    return 0;
+  }
+  const int mode = resolve_weight_mode(weight_mode);
+  if (choose_kernel(kernel, rows, in_features, out_features, bits, dtype, mode) != OQ_KERNEL_TCGEN05) {
+    return 0;
+  }
+  return f16_operand_bytes(rows, in_features) + align_up(static_cast<size_t>(rows) * 4, 256);
+}
 
 int oq_matmul_packed_weight(void *out, const void *x, int dtype, int64_t rows, int64_t in_features,
                             int64_t out_features, const uint8_t *packed, int64_t packed_bytes,
                             int bits, const void *row_norms_bf16, const float *centroids,
                             const void *bias, int bias_dtype, int weight_mode, int kernel,
                             void *workspace, size_t workspace_bytes, void *stream) {
-  (void)workspace;
-  (void)workspace_bytes;
   OQ_CHECK_ARG(bits >= 1 && bits <= 8, "bits must be in [1, 8]");
   OQ_CHECK_ARG(valid_dtype(dtype), "x must be float32, float16, or bfloat16");
   OQ_CHECK_ARG(rows >= 0 && in_features > 0 && out_features >= 0, "negative or empty shape");
@@ -175,16 +206,7 @@ int oq_matmul_packed_weight(void *out, const void *x, int dtype, int64_t rows, i
   }
   const int mode = resolve_weight_mode(weight_mode);
   cudaStream_t s = static_cast<cudaStream_t>(stream);
-  int chosen = kernel;
-  if (chosen == OQ_KERNEL_AUTO) {
-    if (rows <= 16 && small_rows_supported(rows, in_features, out_features, bits, dtype, mode)) {
-      chosen = OQ_KERNEL_SMALL_ROWS;
-    } else if (rows > 16 && tcgen05_gemm_supported(rows, in_features, out_features, bits, dtype, mode)) {
-      chosen = OQ_KERNEL_TCGEN05;
-    } else {
-      chosen = OQ_KERNEL_TILED;
-    }
-  }
+  const int chosen = choose_kernel(kernel, rows, in_features, out_features, bits, dtype, mode);
   switch (chosen) {
     case OQ_KERNEL_SMALL_ROWS:
       if (!small_rows_supported(rows, in_features, out_features, bits, dtype, mode)) {
@@ -198,8 +220,21 @@ int oq_matmul_packed_weight(void *out, const void *x, int dtype, int64_t rows, i
                     "the tcgen05 kernel takes bf16 activations, 4-bit weights, in_features %% 64 == 0 "
                     "and the centroid weight mode");
       }
-      return launch_tcgen05_gemm(out, x, rows, in_features, out_features, packed, row_norms_bf16,
-                                 centroids, bias, bias_dtype, s);
+      {
+        const size_t need = oq_matmul_workspace_bytes(rows, in_features, out_features, bits, dtype,
+                                                      mode, OQ_KERNEL_TCGEN05);
+        if (workspace == nullptr || workspace_bytes < need) {
+          return fail(OQ_ERR_WORKSPACE, "workspace of %zu bytes given, %zu needed", workspace_bytes, need);
+        }
+        OQ_CHECK_ARG(aligned16(workspace), "workspace must be 16-byte aligned");
+        float *row_scale = reinterpret_cast<float *>(static_cast<unsigned char *>(workspace) +
+                                                     f16_operand_bytes(rows, in_features));
+        if (int rc = launch_rows_to_f16(x, dtype, rows, in_features, workspace, row_scale, s)) {
+          return rc;
+        }
+        return launch_tcgen05_gemm(out, workspace, row_scale, rows, in_features, out_features, packed,
+                                   row_norms_bf16, centroids, bias, bias_dtype, s);
+      }
     default:
       return launch_tiled_matmul(out, x, dtype, rows, in_features, out_features, packed, bits,
                                  row_norms_bf16, centroids, bias, bias_dtype, mode, s);
@@ -208,9 +243,16 @@ int oq_matmul_packed_weight(void *out, const void *x, int dtype, int64_t rows, i
 
 size_t oq_linear_workspace_bytes(int64_t rows, int64_t in_features, int64_t out_features,
                                  int weight_bits, int dtype, int weight_mode, int kernel) {
-  const size_t xq = align_up(static_cast<size_t>(rows) * in_features * dtype_size(dtype), 256);
-  return xq + oq_matmul_workspace_bytes(rows, in_features, out_features, weight_bits, dtype,
-                                        weight_mode, kernel);
+  if (rows <= 0 || in_features <= 0 || out_features <= 0) {
+    return 0;
+  }
+  const int mode = resolve_weight_mode(weight_mode);
+  if (choose_kernel(kernel, rows, in_features, out_features, weight_bits, dtype, mode) ==
+      OQ_KERNEL_TCGEN05) {
+    // the prologue writes the f16 operand and its per-token factors straight into it
+    return f16_operand_bytes(rows, in_features) + align_up(static_cast<size_t>(rows) * 4, 256);
+  }
+  return align_up(static_cast<size_t>(rows) * in_features * dtype_size(dtype), 256);
 }
 
 int oq_linear_forward(void *out, const void *x, int dtype, int64_t rows, int64_t in_features,
@@ -222,6 +264,12 @@ int oq_linear_forward(void *out, const void *x, int dtype, int64_t rows, int64_t
                       size_t workspace_bytes, void *stream) {
   OQ_CHECK_ARG(valid_dtype(dtype), "x must be float32, float16, or bfloat16");
   OQ_CHECK_ARG(rows >= 0 && in_features > 0 && out_features >= 0, "negative or empty shape");
+  OQ_CHECK_ARG(weight_bits >= 1 && weight_bits <= 8, "bits must be in [1, 8]");
+  OQ_CHECK_ARG(weight_mode >= OQ_WEIGHT_AUTO && weight_mode <= OQ_WEIGHT_BF16_SCALED,
+               "unknown weight_mode %d", weight_mode);
+  OQ_CHECK_ARG(kernel >= OQ_KERNEL_AUTO && kernel <= OQ_KERNEL_TCGEN05, "unknown kernel %d", kernel);
+  const int64_t needed = (out_features * in_features * weight_bits + 7) / 8;
+  OQ_CHECK_ARG(packed_bytes >= needed, "packed weights are too short");
   if (rows == 0 || out_features == 0) {
     return OQ_OK;
   }
@@ -231,17 +279,35 @@ int oq_linear_forward(void *out, const void *x, int dtype, int64_t rows, int64_t
     return fail(OQ_ERR_WORKSPACE, "workspace of %zu bytes given, %zu needed", workspace_bytes, need);
   }
   OQ_CHECK_ARG(aligned16(workspace), "workspace must be 16-byte aligned");
-  int rc = oq_quantize_activations(x, dtype, rows, in_features, perm, signs, block, act_boundaries,
-                                   act_centroids, act_bits, eps, workspace, nullptr, nullptr, stream);
-  if (rc != OQ_OK) {
+  if (int rc = check_device()) {
     return rc;
   }
-  const size_t xq = align_up(static_cast<size_t>(rows) * in_features * dtype_size(dtype), 256);
+  const int mode = resolve_weight_mode(weight_mode);
+  const int chosen = choose_kernel(kernel, rows, in_features, out_features, weight_bits, dtype, mode);
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (chosen == OQ_KERNEL_TCGEN05) {
+    if (!tcgen05_gemm_supported(rows, in_features, out_features, weight_bits, dtype, mode)) {
+      return fail(OQ_ERR_UNSUPPORTED, "the tcgen05 kernel does not take this problem");
+    }
+    OQ_CHECK_ARG(out && packed && row_norms_bf16 && weight_centroids, "null device pointer");
+    float *row_scale = reinterpret_cast<float *>(static_cast<unsigned char *>(workspace) +
+                                                 f16_operand_bytes(rows, in_features));
+    if (int rc = launch_rotate_quantize(x, dtype, rows, in_features, perm, signs, block,
+                                        act_boundaries, act_centroids, act_bits, eps, workspace,
+                                        nullptr, nullptr, row_scale, s)) {
+      return rc;
+    }
+    return launch_tcgen05_gemm(out, workspace, row_scale, rows, in_features, out_features, packed,
+                               row_norms_bf16, weight_centroids, bias, bias_dtype, s);
+  }
+  if (int rc = launch_rotate_quantize(x, dtype, rows, in_features, perm, signs, block, act_boundaries,
+                                      act_centroids, act_bits, eps, workspace, nullptr, nullptr,
+                                      nullptr, s)) {
+    return rc;
+  }
   return oq_matmul_packed_weight(out, workspace, dtype, rows, in_features, out_features, packed,
                                  packed_bytes, weight_bits, row_norms_bf16, weight_centroids, bias,
-                                 bias_dtype, weight_mode, kernel,
-                                 static_cast<unsigned char *>(workspace) + xq, workspace_bytes - xq,
-                                 stream);
+                                 bias_dtype, weight_mode, chosen, nullptr, 0, stream);
 }
 
 // Status word of the tcgen05 kernel's bounded waits (0 = every wait completed).  Reading

@@ -1,19 +1,26 @@
 // Codebook-decode GEMM for large row counts on the 5th-generation tensor cores.
 //
-//   out[m, n] = (sum_k xq[m, k] * f16(centroid[idx[n, k]] * 2^8)) * row_norm[n] * 2^-8 + bias[n]
+//   out[m, n] = (sum_k a[m, k] * f16(centroid[idx[n, k]] * 2^8)) * row_scale[m] * row_norm[n] * 2^-8
+//               + bias[n],        a[m, k] = f16(xq[m, k] / row_scale[m])
+//
+// tcgen05.mma kind::f16 takes both operands in ONE 16-bit format, and bf16 cannot hold a
+// centroid to better than 2^-9, so both operands are f16: the activations arrive rescaled
+// per token by an exact power of two (written by the rotate-and-quantize prologue in its
+// f16 operand mode, or by rows_to_f16_kernel below for a caller-supplied x) and the factor
+// returns in the epilogue.
 //
 // One CTA computes a 256 x BN output tile (two 128 x BN fp32 accumulators in tensor
 // memory that share every expanded weight tile).  Warp roles:
 //
 //   warp 8 (one lane)  TMA producer: per 64-wide k step, one bulk tensor copy of the
-//                      256 x 64 bf16 activation tile (128-byte swizzle) and one of the
+//                      256 x 64 f16 activation tile (128-byte swizzle) and one of the
 //                      BN x 32-byte packed 4-bit weight tile, both signalling `full[s]`.
 //   warps 0..7         expanders: read the packed tile from shared memory, map every byte
 //                      (two indices) through a shared-memory table of half2 centroid pairs
 //                      and write the BN x 64 f16 operand tile in the 128-byte-swizzled
 //                      K-major layout the MMA descriptor expects; then `bready[s]`.
 //                      After the last k step the same warps run the epilogue.
-//   warp 9 (one lane)  MMA issuer: 2 x 4 tcgen05.mma (128 x BN x 16, bf16 x f16 -> f32)
+//   warp 9 (one lane)  MMA issuer: 2 x 4 tcgen05.mma (128 x BN x 16, f16 x f16 -> f32)
 //                      per k step, tcgen05.commit to `empty[s]`; the last commit signals
 //                      `acc_full`.
 //   epilogue           tcgen05.ld of 32 columns at a time, scale by row_norm[n] * 2^-8,
@@ -58,6 +65,7 @@ struct Tile {
 
 struct GemmParams {
   void *out;
+  const float *row_scale;  // per token: factor the f16 activations were divided by
   const __nv_bfloat16 *row_norms;
   const float *centroids;
   const void *bias;
@@ -194,10 +202,10 @@ __device__ __forceinline__ uint64_t smem_desc_k_sw128(uint32_t addr) {
   return desc;
 }
 
-// Instruction descriptor: f32 accumulator, A = bf16, B = f16, both K-major, M = 128.
+// Instruction descriptor: f32 accumulator, A = B = f16 (format code 0), K-major, M = 128.
 __host__ __device__ constexpr uint32_t instr_desc(int n) {
   return (1u << 4)                             // D format f32
-         | (1u << 7)                           // A format bf16
+         | (0u << 7)                           // A format f16
          | (0u << 10)                          // B format f16
          | (static_cast<uint32_t>(n >> 3) << 17)
          | (static_cast<uint32_t>(128 >> 4) << 24);
@@ -392,6 +400,7 @@ gemm_w4_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
       const int half = warp >> 2;
       const int quarter = warp & 3;
       const int64_t m = m0 + half * 128 + quarter * 32 + lane;
+      const float row_scale = m < p.rows ? p.row_scale[m] : 0.0f;
       const bool vec_ok = (p.out_features % 8) == 0;
       __nv_bfloat16 *out_row = static_cast<__nv_bfloat16 *>(p.out) + m * p.out_features;
 #pragma unroll 1
@@ -403,8 +412,10 @@ gemm_w4_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
           uint32_t packed[16];
 #pragma unroll
           for (int j = 0; j < 16; ++j) {
-            const float a = fmaf(__uint_as_float(v[2 * j]), s_scale[c0 + 2 * j], s_bias[c0 + 2 * j]);
-            const float b = fmaf(__uint_as_float(v[2 * j + 1]), s_scale[c0 + 2 * j + 1], s_bias[c0 + 2 * j + 1]);
+            const float a = fmaf(__uint_as_float(v[2 * j]), row_scale * s_scale[c0 + 2 * j],
+                                 s_bias[c0 + 2 * j]);
+            const float b = fmaf(__uint_as_float(v[2 * j + 1]), row_scale * s_scale[c0 + 2 * j + 1],
+                                 s_bias[c0 + 2 * j + 1]);
             const __nv_bfloat162 h = __floats2bfloat162_rn(a, b);
             packed[j] = *reinterpret_cast<const uint32_t *>(&h);
           }
@@ -434,6 +445,67 @@ gemm_w4_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
   if (warp == kMmaWarp) {
     tc_fence_after();
     tmem_dealloc(tmem_base, T::kTmemCols);
+  }
+}
+
+// Caller-supplied 16-bit activations -> the f16 operand + per-token factor (one warp per
+// token: absolute maximum, exponent, rescale).  bf16/f16 values times a power of two are
+// exact in f16 unless they lie more than 2^28 below the token's maximum.
+template <int DTYPE>
+__global__ void __launch_bounds__(256) rows_to_f16_kernel(const void *x, int64_t rows, int64_t dim,
+                                                          __half *out, float *row_scale) {
+  const int lane = threadIdx.x & 31;
+  const int64_t row = static_cast<int64_t>(blockIdx.x) * 8 + (threadIdx.x >> 5);
+  if (row >= rows) {
+    return;
+  }
+  const uint4 *src = reinterpret_cast<const uint4 *>(static_cast<const uint16_t *>(x) + row * dim);
+  const int vecs = static_cast<int>(dim / 8);
+  uint32_t top = 0;  // largest |x| as raw 15-bit magnitude pattern (monotonic for both formats)
+  for (int i = lane; i < vecs; i += 32) {
+    const uint4 v = __ldg(src + i);
+    const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+      top = max(top, max(w[q] & 0x7fffu, (w[q] >> 16) & 0x7fffu));
+    }
+  }
+#pragma unroll
+  for (int m = 16; m >= 1; m >>= 1) {
+    top = max(top, __shfl_xor_sync(0xffffffffu, top, m));
+  }
+  const float biggest = DTYPE == OQ_DTYPE_BF16 ? bf16_bits_to_float(static_cast<uint16_t>(top))
+                                               : __half2float(__ushort_as_half(static_cast<uint16_t>(top)));
+  float mult = 1.0f;
+  float back = 1.0f;
+  if (biggest > 0.0f && biggest < __int_as_float(0x7f800000)) {
+    const int e = max(ilogbf(biggest) + 1, -100);
+    mult = ldexpf(1.0f, 14 - e);
+    back = ldexpf(1.0f, e - 14);
+  }
+  if (lane == 0) {
+    row_scale[row] = back;
+  }
+  uint4 *dst = reinterpret_cast<uint4 *>(out + row * dim);
+  for (int i = lane; i < vecs; i += 32) {
+    const uint4 v = __ldg(src + i);
+    const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+    uint32_t o[4];
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+      float lo;
+      float hi;
+      if (DTYPE == OQ_DTYPE_BF16) {
+        lo = bf16_bits_to_float(static_cast<uint16_t>(w[q] & 0xffffu));
+        hi = bf16_bits_to_float(static_cast<uint16_t>(w[q] >> 16));
+      } else {
+        lo = __half2float(__ushort_as_half(static_cast<uint16_t>(w[q] & 0xffffu)));
+        hi = __half2float(__ushort_as_half(static_cast<uint16_t>(w[q] >> 16)));
+      }
+      const __half2 h = __floats2half2_rn(lo * mult, hi * mult);
+      o[q] = *reinterpret_cast<const uint32_t *>(&h);
+    }
+    dst[i] = make_uint4(o[0], o[1], o[2], o[3]);
   }
 }
 
@@ -485,10 +557,26 @@ bool tcgen05_gemm_supported(int64_t rows, int64_t in_features, int64_t out_featu
          in_features <= (1 << 30) && rows < (1ll << 31) && out_features < (1ll << 31);
 }
 
-int launch_tcgen05_gemm(void *out, const void *x, int64_t rows, int64_t in_features,
-                        int64_t out_features, const uint8_t *packed, const void *row_norms_bf16,
-                        const float *centroids, const void *bias, int bias_dtype,
-                        cudaStream_t stream) {
+int launch_rows_to_f16(const void *x, int dtype, int64_t rows, int64_t dim, void *out_f16,
+                       float *row_scale, cudaStream_t stream) {
+  OQ_CHECK_ARG(dtype == OQ_DTYPE_BF16 || dtype == OQ_DTYPE_F16, "16-bit activations expected");
+  OQ_CHECK_ARG(dim % 8 == 0 && aligned16(x) && aligned16(out_f16), "rows must be 16-byte aligned");
+  const unsigned grid = static_cast<unsigned>((rows + 7) / 8);
+  if (dtype == OQ_DTYPE_BF16) {
+    rows_to_f16_kernel<OQ_DTYPE_BF16><<<grid, 256, 0, stream>>>(x, rows, dim, static_cast<__half *>(out_f16), row_scale);
+  } else {
+    rows_to_f16_kernel<OQ_DTYPE_F16><<<grid, 256, 0, stream>>>(x, rows, dim, static_cast<__half *>(out_f16), row_scale);
+  }
+  OQ_CHECK_CUDA(cudaGetLastError());
+  count_launch();
+  return OQ_OK;
+}
+
+// `x` is the f16 operand [rows, in_features] and `row_scale` its per-token factor.
+int launch_tcgen05_gemm(void *out, const void *x, const float *row_scale, int64_t rows,
+                        int64_t in_features, int64_t out_features, const uint8_t *packed,
+                        const void *row_norms_bf16, const float *centroids, const void *bias,
+                        int bias_dtype, cudaStream_t stream) {
   OQ_CHECK_ARG(aligned16(x) && aligned16(packed) && aligned16(out),
                "x, packed weights and out must be 16-byte aligned for the tcgen05 kernel");
   EncodeTiledFn encode = encode_tiled_fn();
@@ -519,7 +607,7 @@ int launch_tcgen05_gemm(void *out, const void *x, int64_t rows, int64_t in_featu
     const cuuint64_t strides[1] = {static_cast<cuuint64_t>(in_features) * 2};
     const cuuint32_t box[2] = {kBK, kBM};
     const cuuint32_t elem[2] = {1, 1};
-    const CUresult rc = encode(&map_a, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void *>(x),
+    const CUresult rc = encode(&map_a, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<void *>(x),
                                dims, strides, box, elem, CU_TENSOR_MAP_INTERLEAVE_NONE,
                                CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                                CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
@@ -544,6 +632,7 @@ int launch_tcgen05_gemm(void *out, const void *x, int64_t rows, int64_t in_featu
 
   GemmParams p{};
   p.out = out;
+  p.row_scale = row_scale;
   p.row_norms = static_cast<const __nv_bfloat16 *>(row_norms_bf16);
   p.centroids = centroids;
   p.bias = bias;

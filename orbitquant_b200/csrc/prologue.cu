@@ -42,6 +42,14 @@ struct PrologueParams {
   int rows_per_cta;
   float eps;
   float inv_sqrt_block;
+  // f16 operand mode (16-bit activations only): instead of x_q in x's dtype the kernel
+  // writes half(x_q * 2^(14 - E_row)) with E_row = exponent of the token norm, and the
+  // exact inverse factor 2^(E_row - 14) to row_scale.  x_q is already rounded to x's dtype
+  // (8 or 11 mantissa bits) and |x_q| < norm, so the scaled value is exact in f16 down to
+  // 2^-28 of the norm.  This is the A operand of the tcgen05 kernel, whose MMA needs both
+  // operands in one 16-bit format.
+  int f16_operand;
+  float *row_scale;
 };
 
 // Number of boundaries strictly below `v` (sorted ascending, count = 2^bits - 1), as a
@@ -59,11 +67,17 @@ __device__ __forceinline__ int bucketize(float v, const float *bnd, int bits) {
 template <int DTYPE>
 __device__ __forceinline__ void emit(const PrologueParams &p, void *stage, const float *s_bnd,
                                      const float *s_cent, int64_t row, int r, int i, float v,
-                                     float norm) {
+                                     float norm, float opscale) {
   const float direction = __fmul_rn(v, p.inv_sqrt_block);
   const int idx = bucketize(direction, s_bnd, p.bits);
   const float q = __fmul_rn(s_cent[idx], norm);
-  Scalar<DTYPE>::store(stage, static_cast<int64_t>(r) * p.dim + i, q);
+  if (p.f16_operand) {
+    const float rounded = static_cast<float>(static_cast<typename Scalar<DTYPE>::type>(q));
+    static_cast<__half *>(stage)[static_cast<int64_t>(r) * p.dim + i] =
+        __float2half_rn(__fmul_rn(rounded, opscale));
+  } else {
+    Scalar<DTYPE>::store(stage, static_cast<int64_t>(r) * p.dim + i, q);
+  }
   if (p.codes != nullptr) {
     p.codes[row * p.dim + i] = static_cast<uint8_t>(idx);
   }
@@ -89,7 +103,8 @@ __device__ __forceinline__ void strided_butterflies(float (&v)[S]) {
 template <int DTYPE, int S>
 __device__ __forceinline__ void second_pass(const PrologueParams &p, float *rot, void *stage,
                                             const float *s_bnd, const float *s_cent,
-                                            const float *s_norm, int64_t row_base, int nrows) {
+                                            const float *s_norm, const float *s_opscale,
+                                            int64_t row_base, int nrows) {
   // group g of a row: block b = g / 256, column j = g % 256; values at b*block + j + 256*s.
   const int groups_per_row = p.dim / S;
   const int total = groups_per_row * nrows;
@@ -105,9 +120,10 @@ __device__ __forceinline__ void second_pass(const PrologueParams &p, float *rot,
     }
     strided_butterflies<S>(v);
     const float norm = s_norm[r];
+    const float opscale = s_opscale[r];
 #pragma unroll
     for (int s = 0; s < S; ++s) {
-      emit<DTYPE>(p, stage, s_bnd, s_cent, row_base + r, r, base + s * kChunk, v[s], norm);
+      emit<DTYPE>(p, stage, s_bnd, s_cent, row_base + r, r, base + s * kChunk, v[s], norm, opscale);
     }
   }
 }
@@ -127,6 +143,7 @@ rotate_quantize_kernel(const PrologueParams p) {
   float *s_cent = s_bnd + 256;
   float *s_norm = s_cent + 256;  // [R] norms
   float *s_inv = s_norm + 8;     // [R] 1/(norm+eps)
+  float *s_opscale = s_inv + 8;  // [R] 2^(14 - E) in f16 operand mode
 
   const int levels = 1 << p.bits;
   for (int i = threadIdx.x; i < levels; i += kThreads) {
@@ -194,6 +211,17 @@ rotate_quantize_kernel(const PrologueParams p) {
         s_inv[r] = __fdiv_rn(1.0f, __fadd_rn(norm, p.eps));
         if (p.norms != nullptr) {
           p.norms[row_base + r] = norm;
+        }
+        if (p.f16_operand) {
+          float mult = 1.0f;
+          float back = 1.0f;
+          if (norm > 0.0f && norm < __int_as_float(0x7f800000)) {
+            const int e = max(ilogbf(norm) + 1, -100);
+            mult = ldexpf(1.0f, 14 - e);
+            back = ldexpf(1.0f, e - 14);
+          }
+          s_opscale[r] = mult;
+          p.row_scale[row_base + r] = back;
         }
       }
     }
@@ -265,10 +293,11 @@ rotate_quantize_kernel(const PrologueParams p) {
         }
       } else {
         const float norm = s_norm[r];
+        const float opscale = s_opscale[r];
 #pragma unroll
         for (int e = 0; e < 8; ++e) {
           if (i0 + e < dim) {
-            emit<DTYPE>(p, stage, s_bnd, s_cent, row_base + r, r, i0 + e, v[e], norm);
+            emit<DTYPE>(p, stage, s_bnd, s_cent, row_base + r, r, i0 + e, v[e], norm, opscale);
           }
         }
       }
@@ -278,12 +307,12 @@ rotate_quantize_kernel(const PrologueParams p) {
     // 4. widths >= 256
     if (wide) {
       switch (p.block / kChunk) {
-        case 2: second_pass<DTYPE, 2>(p, rot, stage, s_bnd, s_cent, s_norm, row_base, nrows); break;
-        case 4: second_pass<DTYPE, 4>(p, rot, stage, s_bnd, s_cent, s_norm, row_base, nrows); break;
-        case 8: second_pass<DTYPE, 8>(p, rot, stage, s_bnd, s_cent, s_norm, row_base, nrows); break;
-        case 16: second_pass<DTYPE, 16>(p, rot, stage, s_bnd, s_cent, s_norm, row_base, nrows); break;
-        case 32: second_pass<DTYPE, 32>(p, rot, stage, s_bnd, s_cent, s_norm, row_base, nrows); break;
-        default: second_pass<DTYPE, 64>(p, rot, stage, s_bnd, s_cent, s_norm, row_base, nrows); break;
+        case 2: second_pass<DTYPE, 2>(p, rot, stage, s_bnd, s_cent, s_norm, s_opscale, row_base, nrows); break;
+        case 4: second_pass<DTYPE, 4>(p, rot, stage, s_bnd, s_cent, s_norm, s_opscale, row_base, nrows); break;
+        case 8: second_pass<DTYPE, 8>(p, rot, stage, s_bnd, s_cent, s_norm, s_opscale, row_base, nrows); break;
+        case 16: second_pass<DTYPE, 16>(p, rot, stage, s_bnd, s_cent, s_norm, s_opscale, row_base, nrows); break;
+        case 32: second_pass<DTYPE, 32>(p, rot, stage, s_bnd, s_cent, s_norm, s_opscale, row_base, nrows); break;
+        default: second_pass<DTYPE, 64>(p, rot, stage, s_bnd, s_cent, s_norm, s_opscale, row_base, nrows); break;
       }
       __syncthreads();
     }
@@ -309,7 +338,7 @@ rotate_quantize_kernel(const PrologueParams p) {
 
 size_t prologue_smem_bytes(int dim, int rows_per_cta, int dtype) {
   return ((static_cast<size_t>(rows_per_cta) * dim * (4 + dtype_size(dtype)) + 15) & ~static_cast<size_t>(15)) +
-         (256 + 256 + 16) * 4;
+         (256 + 256 + 24) * 4;
 }
 
 }  // namespace
@@ -320,7 +349,10 @@ constexpr int64_t kMaxBlock = 256 * 64;
 int launch_rotate_quantize(const void *x, int x_dtype, int64_t rows, int64_t dim,
                            const int32_t *perm, const int8_t *signs, int64_t block,
                            const float *boundaries, const float *centroids, int bits, float eps,
-                           void *x_q, uint8_t *codes, float *norms, cudaStream_t stream) {
+                           void *x_q, uint8_t *codes, float *norms, float *f16_row_scale,
+                           cudaStream_t stream) {
+  OQ_CHECK_ARG(f16_row_scale == nullptr || (x_dtype != OQ_DTYPE_F32 && x_q != nullptr),
+               "the f16 operand output needs 16-bit activations and an output buffer");
   OQ_CHECK_ARG(valid_dtype(x_dtype), "x must be float32, float16, or bfloat16");
   OQ_CHECK_ARG(rows >= 0 && dim > 0, "rows must be >= 0 and dim positive");
   OQ_CHECK_ARG(block > 0 && (block & (block - 1)) == 0, "block_size must be a positive power of two");
@@ -329,11 +361,11 @@ int launch_rotate_quantize(const void *x, int x_dtype, int64_t rows, int64_t dim
   OQ_CHECK_ARG(bits >= 1 && bits <= 8, "bits must be in [1, 8]");
   OQ_CHECK_ARG(eps >= 0.0f, "eps must be non-negative");
   OQ_CHECK_ARG(dim <= (1 << 20), "dim above 2^20 is not supported");
-  OQ_CHECK_ARG(x != nullptr && perm != nullptr && signs != nullptr && boundaries != nullptr &&
-                   centroids != nullptr, "null device pointer");
   if (rows == 0) {
     return OQ_OK;
   }
+  OQ_CHECK_ARG(x != nullptr && perm != nullptr && signs != nullptr && boundaries != nullptr &&
+                   centroids != nullptr, "null device pointer");
   OQ_CHECK_ARG(aligned16(x) && (x_q == nullptr || aligned16(x_q)) && aligned16(perm) &&
                    (reinterpret_cast<uintptr_t>(signs) & 7u) == 0,
                "x, x_q and perm must be 16-byte aligned, signs 8-byte aligned");
@@ -380,6 +412,8 @@ int launch_rotate_quantize(const void *x, int x_dtype, int64_t rows, int64_t dim
   p.rows_per_cta = rows_per_cta;
   p.eps = eps;
   p.inv_sqrt_block = static_cast<float>(1.0 / sqrt(static_cast<double>(block)));
+  p.f16_operand = f16_row_scale != nullptr ? 1 : 0;
+  p.row_scale = f16_row_scale;
 
   const int64_t ctas_needed = (rows + rows_per_cta - 1) / rows_per_cta;
   const int grid = static_cast<int>(std::min<int64_t>(ctas_needed, static_cast<int64_t>(sm_count) * 8));
