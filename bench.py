@@ -104,7 +104,7 @@ def synth_activations(rows, k, seed):
     return x.to(torch.bfloat16)
 
 
-def build_layers(workload, device, rank=0, world=1):
+def build_layers(workload, device, rank=0, world=1, rows_override=0):
     from orbitquant_b200 import OrbitQuantConfig, OrbitQuantLinear
     from orbitquant_b200.sharding import shard_linear
 
@@ -119,7 +119,7 @@ def build_layers(workload, device, rank=0, world=1):
         if world > 1:
             module = shard_linear(module, rank, world, config=cfg)
         layers.append((name, k, n, gather, module.to(device)))
-    return rows, layers, w_bits, a_bits
+    return (rows_override or rows), layers, w_bits, a_bits
 
 
 class ClockSampler:
@@ -264,6 +264,8 @@ def main():
     parser.add_argument("--impl", default="ours", choices=["ours", "reference"])
     parser.add_argument("--workload", default="dit_block", choices=sorted(WORKLOADS))
     parser.add_argument("--no-cpu-baseline", action="store_true")
+    parser.add_argument("--rows", type=int, default=0,
+                        help="override the workload's token count (profiling on a smaller case)")
     args = parser.parse_args()
 
     if args.impl == "reference":
@@ -288,7 +290,7 @@ def main():
         dist.init_process_group("nccl", device_id=device)
 
     warmup = max(3, args.warmup)
-    rows, layers, w_bits, a_bits = build_layers(args.workload, device, rank, world)
+    rows, layers, w_bits, a_bits = build_layers(args.workload, device, rank, world, args.rows)
     inputs = [synth_activations(rows, k, WORKLOADS[args.workload][3] * 1000 + i).to(device)
               for i, (_n, k, _N, _g, _m) in enumerate(layers)]
 
@@ -333,22 +335,32 @@ def main():
     peaks = measured_peaks()
     kernel_ms = 0.0
     kernel_launches = 0
-    xqs = []
+    small = rows <= 16
+    prepared = []
     for (name, k, n, gather, module), x in zip(layers, inputs):
-        xqs.append(native.quantize_activations(
+        xq = native.quantize_activations(
             x, module._rotation_permutation, module._rotation_signs,
             module._activation_codebook_centroids, module._activation_codebook_boundaries,
-            eps=module.activation_eps, block_size=module.rotation.block_size))
+            eps=module.activation_eps, block_size=module.rotation.block_size)
+        if small:
+            prepared.append((xq, None))
+        else:
+            prepared.append(native.rows_to_f16_operand(xq))
     torch.cuda.synchronize()
     events = []
     for it in range(args.steps + 2):
-        for (name, k, n, gather, module), xq in zip(layers, xqs):
+        for (name, k, n, gather, module), (operand, scale) in zip(layers, prepared):
             e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             e0.record()
-            native.matmul_packed_weight(xq, module.packed_weight_indices, module.row_norms,
-                                        module._weight_codebook_centroids, bits=w_bits,
-                                        out_features=module.out_features, in_features=k,
-                                        bias=module.bias)
+            if small:
+                native.matmul_packed_weight(operand, module.packed_weight_indices, module.row_norms,
+                                            module._weight_codebook_centroids, bits=w_bits,
+                                            out_features=module.out_features, in_features=k,
+                                            bias=module.bias)
+            else:
+                native.gemm_tcgen05_f16(operand, scale, module.packed_weight_indices,
+                                        module.row_norms, module._weight_codebook_centroids,
+                                        out_features=module.out_features, bias=module.bias)
             e1.record()
             if it >= 2:
                 events.append((e0, e1))
@@ -357,7 +369,6 @@ def main():
         kernel_ms += e0.elapsed_time(e1)
         kernel_launches += 1
     local_flops = sum(layer_flops(rows, k, m.out_features) for _n, k, _N, _g, m in layers)
-    small = rows <= 16
     if small:
         algo_bytes = sum(layer_bytes(rows, k, m.out_features, w_bits, a_bits) for _n, k, _N, _g, m in layers)
         achieved = algo_bytes * args.steps / (kernel_ms * 1e-3) / 1e9

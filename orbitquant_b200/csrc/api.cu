@@ -241,6 +241,41 @@ int oq_matmul_packed_weight(void *out, const void *x, int dtype, int64_t rows, i
   }
 }
 
+int oq_gemm_tcgen05_f16(void *out, const void *x_f16, const float *row_scale, int64_t rows,
+                        int64_t in_features, int64_t out_features, const uint8_t *packed,
+                        int64_t packed_bytes, const void *row_norms_bf16, const float *centroids,
+                        const void *bias, int bias_dtype, void *stream) {
+  OQ_CHECK_ARG(rows >= 0 && in_features > 0 && out_features >= 0, "negative or empty shape");
+  OQ_CHECK_ARG(bias == nullptr || valid_dtype(bias_dtype), "bias must be float32, float16, or bfloat16");
+  OQ_CHECK_ARG(packed_bytes >= (out_features * in_features * 4 + 7) / 8, "packed weights are too short");
+  if (rows == 0 || out_features == 0) {
+    return OQ_OK;
+  }
+  OQ_CHECK_ARG(out && x_f16 && row_scale && packed && row_norms_bf16 && centroids, "null device pointer");
+  if (!tcgen05_gemm_supported(rows, in_features, out_features, 4, OQ_DTYPE_BF16, OQ_WEIGHT_CENTROID)) {
+    return fail(OQ_ERR_UNSUPPORTED, "the tcgen05 kernel needs in_features %% 64 == 0");
+  }
+  if (int rc = check_device()) {
+    return rc;
+  }
+  return launch_tcgen05_gemm(out, x_f16, row_scale, rows, in_features, out_features, packed,
+                             row_norms_bf16, centroids, bias, bias_dtype,
+                             static_cast<cudaStream_t>(stream));
+}
+
+int oq_rows_to_f16_operand(const void *x, int dtype, int64_t rows, int64_t dim, void *x_f16,
+                           float *row_scale, void *stream) {
+  OQ_CHECK_ARG(rows >= 0 && dim > 0, "negative or empty shape");
+  if (rows == 0) {
+    return OQ_OK;
+  }
+  OQ_CHECK_ARG(x && x_f16 && row_scale, "null device pointer");
+  if (int rc = check_device()) {
+    return rc;
+  }
+  return launch_rows_to_f16(x, dtype, rows, dim, x_f16, row_scale, static_cast<cudaStream_t>(stream));
+}
+
 size_t oq_linear_workspace_bytes(int64_t rows, int64_t in_features, int64_t out_features,
                                  int weight_bits, int dtype, int weight_mode, int kernel) {
   if (rows <= 0 || in_features <= 0 || out_features <= 0) {

@@ -15,11 +15,13 @@
 //   warp 8 (one lane)  TMA producer: per 64-wide k step, one bulk tensor copy of the
 //                      256 x 64 f16 activation tile (128-byte swizzle) and one of the
 //                      BN x 32-byte packed 4-bit weight tile, both signalling `full[s]`.
-//   warps 0..7         expanders: read the packed tile from shared memory, map every byte
-//                      (two indices) through a shared-memory table of half2 centroid pairs
-//                      and write the BN x 64 f16 operand tile in the 128-byte-swizzled
-//                      K-major layout the MMA descriptor expects; then `bready[s]`.
-//                      After the last k step the same warps run the epilogue.
+//   warps 0..7         expanders: read the packed tile from shared memory, turn every 4-bit
+//                      index into its f16 centroid with byte-permute lookups in a
+//                      register-resident table (16 entries x 2 bytes = 8 registers; no
+//                      shared-memory table, so no bank conflicts and no LSU traffic for the
+//                      lookup) and write the BN x 64 f16 operand tile in the
+//                      128-byte-swizzled K-major layout the MMA descriptor expects; then
+//                      `bready[s]`.  After the last k step the same warps run the epilogue.
 //   warp 9 (one lane)  MMA issuer: 2 x 4 tcgen05.mma (128 x BN x 16, f16 x f16 -> f32)
 //                      per k step, tcgen05.commit to `empty[s]`; the last commit signals
 //                      `acc_full`.
@@ -31,6 +33,7 @@
 // drained (bounded again), tensor memory is released and the kernel returns.
 #include <cuda.h>
 
+#include <cstdlib>
 #include <mutex>
 
 #include "common.cuh"
@@ -43,9 +46,7 @@ namespace {
 
 constexpr int kBM = 256;
 constexpr int kBK = 64;
-constexpr int kLutRep = 4;
 constexpr int kThreads = 320;
-constexpr int kExpanderWarps = 8;
 constexpr int kProducerWarp = 8;
 constexpr int kMmaWarp = 9;
 constexpr float kCentroidScale = 256.0f;  // f16 operand = centroid * 2^8 (exact scaling)
@@ -53,14 +54,15 @@ constexpr uint32_t kSpinLimit = 1u << 22;
 
 template <int BN>
 struct Tile {
-  static constexpr int kStages = BN == 256 ? 3 : 4;
+  static constexpr int kStages = BN == 128 ? 4 : 3;
   static constexpr int kABytes = kBM * kBK * 2;        // 32 KB
   static constexpr int kBBytes = BN * kBK * 2;         // expanded f16 tile
   static constexpr int kPBytes = BN * (kBK / 2);       // packed 4-bit tile
   static constexpr int kStageBytes = kABytes + kBBytes + kPBytes;
-  static constexpr int kHeaderBytes = 256 /*barriers*/ + 2 * BN * 4 /*scale,bias*/ + 256 * kLutRep * 4;
+  static constexpr int kHeaderBytes = 256 /*barriers*/ + 2 * BN * 4 /*scale,bias*/;
   static constexpr int kSmemBytes = kHeaderBytes + 1024 /*alignment slack*/ + kStages * kStageBytes;
-  static constexpr int kTmemCols = 2 * BN;
+  static constexpr int kTmemCols = BN == 128 ? 256 : 512;  // power of two >= 2 * BN
+  static constexpr int kExpanderWarps = BN == 128 ? 8 : BN / 32;  // warps that own weight rows
 };
 
 struct GemmParams {
@@ -219,19 +221,43 @@ __device__ __forceinline__ float load_bias(const void *bias, int dtype, int64_t 
   }
 }
 
+// Eight 4-bit indices (one 32-bit word of the stream, lowest k in the low nibble) -> eight
+// f16 table entries, in k order.  prmt picks one of 8 bytes with a 3-bit selector, so the
+// 16-entry table is looked up as two 8-entry halves and bit 3 of the index chooses between
+// them through a byte mask (itself a prmt of the constant 0x0000ff00).
+__device__ __forceinline__ void decode8(uint32_t w, const uint32_t (&tab_hi)[4],
+                                        const uint32_t (&tab_lo)[4], uint4 &out) {
+  const uint32_t low3 = w & 0x77777777u;
+  const uint32_t bit3 = (w >> 3) & 0x11111111u;
+  uint32_t r[4];
+#pragma unroll
+  for (int h = 0; h < 2; ++h) {
+    const uint32_t sel = low3 >> (16 * h);
+    const uint32_t mask = __byte_perm(0x0000ff00u, 0u, bit3 >> (16 * h));
+    const uint32_t hx = __byte_perm(tab_hi[0], tab_hi[1], sel);
+    const uint32_t hy = __byte_perm(tab_hi[2], tab_hi[3], sel);
+    const uint32_t lx = __byte_perm(tab_lo[0], tab_lo[1], sel);
+    const uint32_t ly = __byte_perm(tab_lo[2], tab_lo[3], sel);
+    const uint32_t hi = (hx & ~mask) | (hy & mask);
+    const uint32_t lo = (lx & ~mask) | (ly & mask);
+    r[2 * h] = __byte_perm(lo, hi, 0x5140u);
+    r[2 * h + 1] = __byte_perm(lo, hi, 0x7362u);
+  }
+  out = make_uint4(r[0], r[1], r[2], r[3]);
+}
+
 template <int BN>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_w4_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
                        const __grid_constant__ CUtensorMap map_p, const GemmParams p) {
   using T = Tile<BN>;
   extern __shared__ __align__(16) unsigned char smem_raw[];
-  // header: barriers | scale[BN] | bias[BN] | lut[256*rep]
+  // header: barriers | scale[BN] | bias[BN]
   uint64_t *bars = reinterpret_cast<uint64_t *>(smem_raw);
   uint32_t *s_tmem = reinterpret_cast<uint32_t *>(smem_raw + 192);
   volatile int *s_abort = reinterpret_cast<volatile int *>(smem_raw + 200);
   float *s_scale = reinterpret_cast<float *>(smem_raw + 256);
   float *s_bias = s_scale + BN;
-  uint32_t *s_lut = reinterpret_cast<uint32_t *>(s_bias + BN);
   const uint32_t header_end = smem_u32(smem_raw) + T::kHeaderBytes;
   const uint32_t stage_base = (header_end + 1023u) & ~1023u;
   unsigned char *stage_ptr = smem_raw + (stage_base - smem_u32(smem_raw));
@@ -257,7 +283,7 @@ gemm_w4_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
     for (int s = 0; s < T::kStages; ++s) {
       mbar_init(full_bar(s), 1);
       mbar_init(empty_bar(s), 1);
-      mbar_init(bready_bar(s), kExpanderWarps);
+      mbar_init(bready_bar(s), T::kExpanderWarps);
     }
     mbar_init(acc_full_bar, 1);
     *s_abort = 0;
@@ -269,17 +295,6 @@ gemm_w4_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
   if (warp == kProducerWarp && lane == 0) {
     asm volatile("prefetch.tensormap [%0];" ::"l"(&map_a) : "memory");
     asm volatile("prefetch.tensormap [%0];" ::"l"(&map_p) : "memory");
-  }
-  // Byte -> (centroid[lo], centroid[hi]) * 2^8 as half2, replicated kLutRep times.
-  for (int v = threadIdx.x; v < 256; v += kThreads) {
-    const __half lo = __float2half_rn(p.centroids[v & 15] * kCentroidScale);
-    const __half hi = __float2half_rn(p.centroids[v >> 4] * kCentroidScale);
-    const uint32_t word = static_cast<uint32_t>(__half_as_ushort(lo)) |
-                          (static_cast<uint32_t>(__half_as_ushort(hi)) << 16);
-#pragma unroll
-    for (int c = 0; c < kLutRep; ++c) {
-      s_lut[v * kLutRep + c] = word;
-    }
   }
   for (int i = threadIdx.x; i < BN; i += kThreads) {
     const int64_t n = n0 + i;
@@ -346,16 +361,32 @@ gemm_w4_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
     }
   } else {
     // ---- expanders ----
-    constexpr int kThreadsPerRow = 256 / BN;          // 1 (BN=256) or 2 (BN=128)
+    constexpr int kThreadsPerRow = BN == 128 ? 2 : 1;  // BN=192 leaves warps 6 and 7 without rows
     constexpr int kBytesPerThread = 32 / kThreadsPerRow;
     constexpr int kChunksPerThread = kBytesPerThread / 4;
     const int et = threadIdx.x;  // 0..255
     const int row = et / kThreadsPerRow;
     const int part = et % kThreadsPerRow;
-    const uint32_t *lut = s_lut + (lane & (kLutRep - 1));
+    // Register table: entry i = f16(centroid[i] * 2^8); hi/lo bytes of entries 4q..4q+3.
+    uint32_t tab_hi[4];
+    uint32_t tab_lo[4];
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+      uint32_t hi = 0;
+      uint32_t lo = 0;
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const uint32_t bits = __half_as_ushort(__float2half_rn(p.centroids[4 * q + e] * kCentroidScale));
+        hi |= (bits >> 8) << (8 * e);
+        lo |= (bits & 0xffu) << (8 * e);
+      }
+      tab_hi[q] = hi;
+      tab_lo[q] = lo;
+    }
     const uint32_t row_off = (row >> 3) * 1024 + (row & 7) * 128;
     bool ok = true;
-    for (int it = 0; it < p.k_iters; ++it) {
+    const int expand_iters = warp < T::kExpanderWarps ? p.k_iters : 0;
+    for (int it = 0; it < expand_iters; ++it) {
       const int s = it % T::kStages;
       const uint32_t phase = (it / T::kStages) & 1u;
       if (!mbar_wait(full_bar(s), phase, s_abort, 4)) {
@@ -375,12 +406,8 @@ gemm_w4_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
       const uint32_t dst_row = b_addr(s) + row_off;
 #pragma unroll
       for (int c = 0; c < kChunksPerThread; ++c) {
-        const uint32_t w = words[c];
         uint4 o;
-        o.x = lut[(w & 0xffu) * kLutRep];
-        o.y = lut[((w >> 8) & 0xffu) * kLutRep];
-        o.z = lut[((w >> 16) & 0xffu) * kLutRep];
-        o.w = lut[(w >> 24) * kLutRep];
+        decode8(words[c], tab_hi, tab_lo, o);
         const int chunk = part * kChunksPerThread + c;
         const uint32_t dst = dst_row + (((chunk ^ (row & 7)) & 7) << 4);
         asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(dst), "r"(o.x), "r"(o.y),
@@ -588,15 +615,33 @@ int launch_tcgen05_gemm(void *out, const void *x, const float *row_scale, int64_
   OQ_CHECK_CUDA(cudaGetDevice(&device));
   OQ_CHECK_CUDA(cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, device));
 
-  // Tile width: prefer 256 columns (less shared-memory traffic per flop) unless the last
-  // wave of 256-wide tiles would leave much of the machine idle and 128 fills it better.
+  // Tile width.  Wider tiles move fewer shared-memory bytes per flop (the activation tile
+  // is re-read once per MMA), narrower ones can fill the last wave better; pick the width
+  // with the best product of the two.  The per-width rates are measured ratios.
   const int64_t m_tiles = (rows + kBM - 1) / kBM;
-  auto wave_efficiency = [&](int bn) {
-    const int64_t tiles = m_tiles * ((out_features + bn - 1) / bn);
+  auto score = [&](int width, double rate) {
+    const int64_t tiles = m_tiles * ((out_features + width - 1) / width);
     const int64_t waves = (tiles + sm_count - 1) / sm_count;
-    return static_cast<double>(tiles) / static_cast<double>(waves * sm_count);
+    const double useful = static_cast<double>(out_features) /
+                          static_cast<double>(((out_features + width - 1) / width) * width);
+    return rate * useful * static_cast<double>(tiles) / static_cast<double>(waves * sm_count);
   };
-  const int bn = (out_features <= 128 || wave_efficiency(128) > wave_efficiency(256) + 0.08) ? 128 : 256;
+  int bn = 256;
+  double best = score(256, 1.0);
+  if (score(192, 0.93) > best) {
+    bn = 192;
+    best = score(192, 0.93);
+  }
+  if (score(128, 0.76) > best) {
+    bn = 128;
+  }
+  // ORBIT_B200_TILE_N=128|192|256 pins the width (tests and profiling).
+  if (const char *forced = getenv("ORBIT_B200_TILE_N")) {
+    const int value = atoi(forced);
+    if (value == 128 || value == 192 || value == 256) {
+      bn = value;
+    }
+  }
   const int64_t n_tiles = (out_features + bn - 1) / bn;
   OQ_CHECK_ARG(m_tiles * n_tiles < (1ll << 31), "too many output tiles");
 
@@ -642,8 +687,11 @@ int launch_tcgen05_gemm(void *out, const void *x, const float *row_scale, int64_
   p.k_iters = static_cast<int>(in_features / kBK);
   p.m_tiles = static_cast<int>(m_tiles);
   const int grid = static_cast<int>(m_tiles * n_tiles);
-  return bn == 256 ? launch_bn<256>(map_a, map_p, p, grid, stream)
-                   : launch_bn<128>(map_a, map_p, p, grid, stream);
+  switch (bn) {
+    case 256: return launch_bn<256>(map_a, map_p, p, grid, stream);
+    case 192: return launch_bn<192>(map_a, map_p, p, grid, stream);
+    default: return launch_bn<128>(map_a, map_p, p, grid, stream);
+  }
 }
 
 int read_gemm_status(int *status) {

@@ -55,7 +55,25 @@ struct PrologueParams {
 // Number of boundaries strictly below `v` (sorted ascending, count = 2^bits - 1), as a
 // branch-free binary search.  `!(v <= b)` keeps the reference's treatment of NaN (counts
 // as above every boundary).
+template <int BITS>
+__device__ __forceinline__ int bucketize_fixed(float v, const float *bnd) {
+  int pos = 0;
+#pragma unroll
+  for (int step = 1 << (BITS - 1); step >= 1; step >>= 1) {
+    pos += !(v <= bnd[pos + step - 1]) ? step : 0;
+  }
+  return pos;
+}
+
 __device__ __forceinline__ int bucketize(float v, const float *bnd, int bits) {
+  switch (bits) {  // uniform across the grid
+    case 4: return bucketize_fixed<4>(v, bnd);
+    case 3: return bucketize_fixed<3>(v, bnd);
+    case 6: return bucketize_fixed<6>(v, bnd);
+    case 2: return bucketize_fixed<2>(v, bnd);
+    case 8: return bucketize_fixed<8>(v, bnd);
+    default: break;
+  }
   int pos = 0;
 #pragma unroll 1
   for (int step = 1 << (bits - 1); step >= 1; step >>= 1) {
@@ -65,21 +83,20 @@ __device__ __forceinline__ int bucketize(float v, const float *bnd, int bits) {
 }
 
 template <int DTYPE>
-__device__ __forceinline__ void emit(const PrologueParams &p, void *stage, const float *s_bnd,
-                                     const float *s_cent, int64_t row, int r, int i, float v,
+__device__ __forceinline__ void emit(const PrologueParams &p, void *stage_row, uint8_t *codes_row,
+                                     const float *s_bnd, const float *s_cent, int i, float v,
                                      float norm, float opscale) {
   const float direction = __fmul_rn(v, p.inv_sqrt_block);
   const int idx = bucketize(direction, s_bnd, p.bits);
   const float q = __fmul_rn(s_cent[idx], norm);
   if (p.f16_operand) {
     const float rounded = static_cast<float>(static_cast<typename Scalar<DTYPE>::type>(q));
-    static_cast<__half *>(stage)[static_cast<int64_t>(r) * p.dim + i] =
-        __float2half_rn(__fmul_rn(rounded, opscale));
+    static_cast<__half *>(stage_row)[i] = __float2half_rn(__fmul_rn(rounded, opscale));
   } else {
-    Scalar<DTYPE>::store(stage, static_cast<int64_t>(r) * p.dim + i, q);
+    Scalar<DTYPE>::store(stage_row, i, q);
   }
-  if (p.codes != nullptr) {
-    p.codes[row * p.dim + i] = static_cast<uint8_t>(idx);
+  if (codes_row != nullptr) {
+    codes_row[i] = static_cast<uint8_t>(idx);
   }
 }
 
@@ -100,36 +117,67 @@ __device__ __forceinline__ void strided_butterflies(float (&v)[S]) {
   }
 }
 
-template <int DTYPE, int S>
-__device__ __forceinline__ void second_pass(const PrologueParams &p, float *rot, void *stage,
-                                            const float *s_bnd, const float *s_cent,
-                                            const float *s_norm, const float *s_opscale,
-                                            int64_t row_base, int nrows) {
-  // group g of a row: block b = g / 256, column j = g % 256; values at b*block + j + 256*s.
-  const int groups_per_row = p.dim / S;
-  const int total = groups_per_row * nrows;
-  for (int item = threadIdx.x; item < total; item += kThreads) {
-    const int r = item / groups_per_row;
-    const int g = item - r * groups_per_row;
-    const int base = (g / kChunk) * p.block + (g % kChunk);
-    float *src = rot + static_cast<int64_t>(r) * p.dim + base;
-    float v[S];
-#pragma unroll
-    for (int s = 0; s < S; ++s) {
-      v[s] = src[s * kChunk];
-    }
-    strided_butterflies<S>(v);
+// One pass over butterfly widths stride, 2*stride, ..., stride*S/2: a thread owns the S values
+// `stride` apart of one group.  With LAST the results are quantised and staged, otherwise
+// they return to `rot` for the next pass (the caller synchronises in between).
+template <int DTYPE, int S, bool LAST>
+__device__ __forceinline__ void strided_pass(const PrologueParams &p, float *rot, void *stage,
+                                             const float *s_bnd, const float *s_cent,
+                                             const float *s_norm, const float *s_opscale,
+                                             int64_t row_base, int nrows, int stride) {
+  // A row splits into dim/(stride*S) super-groups of stride*S contiguous values; inside one,
+  // column j in [0, stride) and s in [0, S) address value j + stride*s.  stride is a
+  // multiple of 256 and a power of two, so thread t owns the columns congruent to t mod 256
+  // and the index arithmetic is shifts and masks.
+  const int sq_log2 = __ffs(stride / kChunk) - 1;
+  const int sq_mask = (stride / kChunk) - 1;
+  const int cols = p.dim / (S * kChunk);
+  constexpr int kElem = static_cast<int>(sizeof(typename Scalar<DTYPE>::type));
+  for (int r = 0; r < nrows; ++r) {
+    float *row = rot + r * p.dim;
+    void *stage_row = static_cast<unsigned char *>(stage) + static_cast<size_t>(r) * p.dim * kElem;
+    uint8_t *codes_row = p.codes == nullptr ? nullptr : p.codes + (row_base + r) * p.dim;
     const float norm = s_norm[r];
     const float opscale = s_opscale[r];
+    for (int c = 0; c < cols; ++c) {
+      const int base = (c >> sq_log2) * (stride * S) + (c & sq_mask) * kChunk + static_cast<int>(threadIdx.x);
+      float *src = row + base;
+      float v[S];
 #pragma unroll
-    for (int s = 0; s < S; ++s) {
-      emit<DTYPE>(p, stage, s_bnd, s_cent, row_base + r, r, base + s * kChunk, v[s], norm, opscale);
+      for (int s = 0; s < S; ++s) {
+        v[s] = src[s * stride];
+      }
+      strided_butterflies<S>(v);
+      if (LAST) {
+#pragma unroll
+        for (int s = 0; s < S; ++s) {
+          emit<DTYPE>(p, stage_row, codes_row, s_bnd, s_cent, base + s * stride, v[s], norm, opscale);
+        }
+      } else {
+#pragma unroll
+        for (int s = 0; s < S; ++s) {
+          src[s * stride] = v[s];
+        }
+      }
     }
   }
 }
 
+template <int DTYPE, bool LAST>
+__device__ __forceinline__ void strided_pass_any(const PrologueParams &p, float *rot, void *stage,
+                                                 const float *s_bnd, const float *s_cent,
+                                                 const float *s_norm, const float *s_opscale,
+                                                 int64_t row_base, int nrows, int stride, int radix) {
+  switch (radix) {
+    case 2: strided_pass<DTYPE, 2, LAST>(p, rot, stage, s_bnd, s_cent, s_norm, s_opscale, row_base, nrows, stride); break;
+    case 4: strided_pass<DTYPE, 4, LAST>(p, rot, stage, s_bnd, s_cent, s_norm, s_opscale, row_base, nrows, stride); break;
+    case 8: strided_pass<DTYPE, 8, LAST>(p, rot, stage, s_bnd, s_cent, s_norm, s_opscale, row_base, nrows, stride); break;
+    default: strided_pass<DTYPE, 16, LAST>(p, rot, stage, s_bnd, s_cent, s_norm, s_opscale, row_base, nrows, stride); break;
+  }
+}
+
 template <int DTYPE>
-__global__ void __launch_bounds__(kThreads)
+__global__ void __launch_bounds__(kThreads, 3)
 rotate_quantize_kernel(const PrologueParams p) {
   using elem_t = typename Scalar<DTYPE>::type;
   extern __shared__ __align__(16) unsigned char smem[];
@@ -191,7 +239,19 @@ rotate_quantize_kernel(const PrologueParams p) {
       if (r < nrows) {
         const elem_t *xr = xin + static_cast<size_t>(r) * dim;
         const int full = dim & ~15;
-        for (int i = j; i < full; i += 16) {
+        int i = j;
+        for (; i + 7 * 16 < full; i += 8 * 16) {
+          float v[8];
+#pragma unroll
+          for (int u = 0; u < 8; ++u) {
+            v[u] = static_cast<float>(xr[i + 16 * u]);
+          }
+#pragma unroll
+          for (int u = 0; u < 8; ++u) {
+            acc = __fmaf_rn(v[u], v[u], acc);
+          }
+        }
+        for (; i < full; i += 16) {
           const float v = static_cast<float>(xr[i]);
           acc = __fmaf_rn(v, v, acc);
         }
@@ -243,9 +303,11 @@ rotate_quantize_kernel(const PrologueParams p) {
         const int pi[8] = {pa.x, pa.y, pa.z, pa.w, pb.x, pb.y, pb.z, pb.w};
 #pragma unroll
         for (int e = 0; e < 8; ++e) {
-          const int sbyte = ((e < 4 ? sg.x : sg.y) >> (8 * (e & 3))) & 0xff;
-          const float sign = static_cast<float>(static_cast<signed char>(sbyte));
-          v[e] = __fmul_rn(__fmul_rn(static_cast<float>(xr[pi[e]]), sign), inv);
+          // x * (+-1) is exact: flip the sign bit where the sign byte is negative
+          const uint32_t word = static_cast<uint32_t>(e < 4 ? sg.x : sg.y);
+          const uint32_t flip = (word << (24 - 8 * (e & 3))) & 0x80000000u;
+          const float signed_x = __uint_as_float(__float_as_uint(static_cast<float>(xr[pi[e]])) ^ flip);
+          v[e] = __fmul_rn(signed_x, inv);
         }
       } else {
 #pragma unroll
@@ -277,11 +339,13 @@ rotate_quantize_kernel(const PrologueParams p) {
 #pragma unroll
       for (int m = 1; m < 32; m <<= 1) {
         if (m * 8 < p.block) {
-          const bool upper = (lane & m) != 0;
+          // lower lane: v + other; upper lane: other - v.  (+-1)*v is exact, so one fused
+          // multiply-add rounds exactly like the add / subtract it replaces.
+          const float sgn = (lane & m) != 0 ? -1.0f : 1.0f;
 #pragma unroll
           for (int e = 0; e < 8; ++e) {
             const float other = __shfl_xor_sync(0xffffffffu, v[e], m);
-            v[e] = upper ? __fsub_rn(other, v[e]) : __fadd_rn(v[e], other);
+            v[e] = __fmaf_rn(sgn, v[e], other);
           }
         }
       }
@@ -294,26 +358,29 @@ rotate_quantize_kernel(const PrologueParams p) {
       } else {
         const float norm = s_norm[r];
         const float opscale = s_opscale[r];
+        void *stage_row = static_cast<unsigned char *>(stage) + static_cast<size_t>(r) * dim * sizeof(elem_t);
+        uint8_t *codes_row = p.codes == nullptr ? nullptr : p.codes + (row_base + r) * dim;
 #pragma unroll
         for (int e = 0; e < 8; ++e) {
           if (i0 + e < dim) {
-            emit<DTYPE>(p, stage, s_bnd, s_cent, row_base + r, r, i0 + e, v[e], norm, opscale);
+            emit<DTYPE>(p, stage_row, codes_row, s_bnd, s_cent, i0 + e, v[e], norm, opscale);
           }
         }
       }
     }
     __syncthreads();
 
-    // 4. widths >= 256
+    // 4. widths >= 256: radix-16 passes in registers, the last one quantises
     if (wide) {
-      switch (p.block / kChunk) {
-        case 2: second_pass<DTYPE, 2>(p, rot, stage, s_bnd, s_cent, s_norm, s_opscale, row_base, nrows); break;
-        case 4: second_pass<DTYPE, 4>(p, rot, stage, s_bnd, s_cent, s_norm, s_opscale, row_base, nrows); break;
-        case 8: second_pass<DTYPE, 8>(p, rot, stage, s_bnd, s_cent, s_norm, s_opscale, row_base, nrows); break;
-        case 16: second_pass<DTYPE, 16>(p, rot, stage, s_bnd, s_cent, s_norm, s_opscale, row_base, nrows); break;
-        case 32: second_pass<DTYPE, 32>(p, rot, stage, s_bnd, s_cent, s_norm, s_opscale, row_base, nrows); break;
-        default: second_pass<DTYPE, 64>(p, rot, stage, s_bnd, s_cent, s_norm, s_opscale, row_base, nrows); break;
+      int stride = kChunk;
+      while (p.block / stride > 16) {
+        strided_pass_any<DTYPE, false>(p, rot, stage, s_bnd, s_cent, s_norm, s_opscale, row_base,
+                                       nrows, stride, 16);
+        stride *= 16;
+        __syncthreads();
       }
+      strided_pass_any<DTYPE, true>(p, rot, stage, s_bnd, s_cent, s_norm, s_opscale, row_base, nrows,
+                                    stride, p.block / stride);
       __syncthreads();
     }
 
@@ -343,8 +410,8 @@ size_t prologue_smem_bytes(int dim, int rows_per_cta, int dtype) {
 
 }  // namespace
 
-// Largest block the two-pass scheme covers: 256 (warp) x 64 (registers).
-constexpr int64_t kMaxBlock = 256 * 64;
+// Blocks of any power of two up to the dim limit: 256 (warp) x 16 per register pass.
+constexpr int64_t kMaxBlock = 1 << 20;
 
 int launch_rotate_quantize(const void *x, int x_dtype, int64_t rows, int64_t dim,
                            const int32_t *perm, const int8_t *signs, int64_t block,
@@ -382,7 +449,7 @@ int launch_rotate_quantize(const void *x, int x_dtype, int64_t rows, int64_t dim
   const int chunks = static_cast<int>((dim + kChunk - 1) / kChunk);
   int rows_per_cta = 1;
   for (int r = 1; r <= 8; r *= 2) {
-    if (prologue_smem_bytes(static_cast<int>(dim), r, x_dtype) > 96 * 1024 ||
+    if (prologue_smem_bytes(static_cast<int>(dim), r, x_dtype) > 72 * 1024 ||
         static_cast<int64_t>(r) * sm_count > rows) {
       break;
     }

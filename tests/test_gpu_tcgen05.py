@@ -41,6 +41,38 @@ def test_tcgen05_vs_oracle(oracle, rows, k, n):
     _check_close(y, ref, (rows, k, n))
 
 
+@pytest.mark.parametrize("tile_n", ["128", "192", "256"])
+def test_tcgen05_every_tile_width(oracle, tile_n, monkeypatch):
+    dev = _dev()
+    monkeypatch.setenv("ORBIT_B200_TILE_N", tile_n)
+    native.gemm_clear_device_status()
+    rows, k, n = 520, 512, 840          # ragged in M and in N for every width
+    idx, packed, rn, bias = _random_layer(k, n, 4, seed=int(tile_n))
+    cent = get_codebook(k, 4).centroids
+    x = (torch.randn(rows, k) * 0.7).to(torch.bfloat16)
+    y = _run(x.to(dev), packed.to(dev), rn, cent, n, k, bias, native.KERNEL_TCGEN05)
+    _assert_status_clean()
+    ref, _ = oracle.matmul_packed(x, packed, rn, cent, bits=4, out_features=n, bias=bias,
+                                  mode=oracle.MM_FP32_CENTROIDS)
+    _check_close(y, ref, ("tile", tile_n))
+
+
+def test_f16_operand_rescaling_is_exact():
+    """Token scales spanning 2^-40 .. 2^40 must not change the result beyond the scale."""
+    dev = _dev()
+    k, n, rows = 256, 64, 40
+    idx, packed, rn, _ = _random_layer(k, n, 4, seed=3, bias=False)
+    cent = get_codebook(k, 4).centroids
+    base = torch.randn(rows, k).to(torch.bfloat16)
+    scales = torch.tensor([2.0 ** e for e in range(-40, 40, 2)])[:, None]
+    y1 = _run(base.to(dev), packed.to(dev), rn, cent, n, k, None, native.KERNEL_TCGEN05).float().cpu()
+    y2 = _run((base.float() * scales).to(torch.bfloat16).to(dev), packed.to(dev), rn, cent, n, k, None,
+              native.KERNEL_TCGEN05).float().cpu()
+    assert torch.allclose(y2 / scales, y1, rtol=1e-2, atol=0)   # bf16 output rounding only
+    operand, factor = native.rows_to_f16_operand(base.to(dev))
+    assert torch.equal((operand.float() * factor[:, None]).cpu(), base.float())
+
+
 def test_tcgen05_structured_inputs_catch_layout_errors():
     """One-hot activations pick out single weight columns, so any swizzle / descriptor /
     nibble-order mistake shows up as a wrong exact value rather than as noise."""
