@@ -403,6 +403,26 @@ rotate_quantize_kernel(const PrologueParams p) {
   }
 }
 
+}  // namespace
+}  // namespace oq
+
+#include "prologue_fast.cuh"
+
+namespace oq {
+namespace {
+
+template <bool F16OP>
+void (*fast_kernel_for(int bits))(PrologueParams) {
+  switch (bits) {
+    case 2: return rotate_quantize_fast_kernel<2, F16OP>;
+    case 3: return rotate_quantize_fast_kernel<3, F16OP>;
+    case 4: return rotate_quantize_fast_kernel<4, F16OP>;
+    case 6: return rotate_quantize_fast_kernel<6, F16OP>;
+    case 8: return rotate_quantize_fast_kernel<8, F16OP>;
+    default: return nullptr;
+  }
+}
+
 size_t prologue_smem_bytes(int dim, int rows_per_cta, int dtype) {
   return ((static_cast<size_t>(rows_per_cta) * dim * (4 + dtype_size(dtype)) + 15) & ~static_cast<size_t>(15)) +
          (256 + 256 + 24) * 4;
@@ -444,12 +464,18 @@ int launch_rotate_quantize(const void *x, int x_dtype, int64_t rows, int64_t dim
   OQ_CHECK_CUDA(cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, device));
   OQ_CHECK_CUDA(cudaDeviceGetAttribute(&max_smem, cudaDevAttrMaxSharedMemoryPerBlockOptin, device));
 
+  void (*fast)(PrologueParams) = nullptr;
+  if (x_dtype == OQ_DTYPE_BF16 && dim % 256 == 0 && block >= 256 && codes == nullptr &&
+      norms == nullptr && x_q != nullptr) {
+    fast = f16_row_scale != nullptr ? fast_kernel_for<true>(bits) : fast_kernel_for<false>(bits);
+  }
+
   // Rows per CTA: enough (row, chunk) items to fill the 8 warps evenly, within ~96 KB so
   // two CTAs share an SM, and never more than the problem offers per SM.
   const int chunks = static_cast<int>((dim + kChunk - 1) / kChunk);
   int rows_per_cta = 1;
   for (int r = 1; r <= 8; r *= 2) {
-    if (prologue_smem_bytes(static_cast<int>(dim), r, x_dtype) > 72 * 1024 ||
+    if (prologue_smem_bytes(static_cast<int>(dim), r, x_dtype) > (fast != nullptr ? 52 : 72) * 1024 ||
         static_cast<int64_t>(r) * sm_count > rows) {
       break;
     }
@@ -458,7 +484,8 @@ int launch_rotate_quantize(const void *x, int x_dtype, int64_t rows, int64_t dim
       break;
     }
   }
-  const size_t smem = prologue_smem_bytes(static_cast<int>(dim), rows_per_cta, x_dtype);
+  const size_t smem = fast != nullptr ? fast_smem_bytes(static_cast<int>(dim), rows_per_cta, bits)
+                                      : prologue_smem_bytes(static_cast<int>(dim), rows_per_cta, x_dtype);
   OQ_CHECK_ARG(smem <= static_cast<size_t>(max_smem),
                "dim %lld needs %zu bytes of shared memory per token (limit %d)", (long long)dim,
                smem, max_smem);
@@ -489,6 +516,9 @@ int launch_rotate_quantize(const void *x, int x_dtype, int64_t rows, int64_t dim
     case OQ_DTYPE_F32: kernel = rotate_quantize_kernel<OQ_DTYPE_F32>; break;
     case OQ_DTYPE_F16: kernel = rotate_quantize_kernel<OQ_DTYPE_F16>; break;
     default: kernel = rotate_quantize_kernel<OQ_DTYPE_BF16>; break;
+  }
+  if (fast != nullptr) {
+    kernel = fast;
   }
   if (smem > 48 * 1024) {
     OQ_CHECK_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,

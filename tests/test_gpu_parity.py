@@ -119,6 +119,10 @@ def test_prologue_bit_exact_vs_oracle(oracle, golden_codebooks, rows, dim, block
     assert torch.equal(bits_of(xq), bits_of(xq_ref)), "quantised activations differ"
     if rows > 2:
         assert torch.all(xq[rows // 2] == 0)
+    # without the side outputs the specialised kernel runs (bf16, dim % 256 == 0, block >= 256)
+    xq_only = native.quantize_activations(x.to(dev), rot.permutation, rot.signs, cb.centroids,
+                                          cb.boundaries, eps=1e-10, block_size=block)
+    assert torch.equal(bits_of(xq_only), bits_of(xq_ref)), "specialised kernel differs"
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.float16])
