@@ -179,6 +179,35 @@ int oq_linear_forward(void *out, const void *x, int dtype, int64_t rows, int64_t
 size_t oq_linear_workspace_bytes(int64_t rows, int64_t in_features, int64_t out_features,
                                  int weight_bits, int dtype, int weight_mode, int kernel);
 
+/* ---- no-allocation variant ------------------------------------------------------------ */
+
+/* oq_linear_forward for callers that cannot allocate device memory at all -- plugin code
+ * running inside another runtime's enqueue callback, programs that gave all GPU memory to
+ * one pool at start-up.  Same arguments as oq_linear_forward without the workspace: the
+ * scratch for the quantised activations is a fixed 4 MiB device array inside the library
+ * image (oq_static_scratch_bytes()), so the call performs no cudaMalloc / cudaFree and uses
+ * no allocating library routine.  This entry point has no counterpart in the reference.
+ *
+ *  - Limit: oq_linear_workspace_bytes(...) for the problem must not exceed
+ *    oq_static_scratch_bytes() (about rows * in_features * 2 <= 4 MiB, e.g. 128 tokens of
+ *    16384 features); larger problems return OQ_ERR_WORKSPACE with a message and run nothing.
+ *  - Cost: every GPU on which the library is loaded holds the 4 MiB until the process exits.
+ *  - The first call on each device looks the array's device address up
+ *    (cudaGetSymbolAddress, with that device current) and caches it; make that first call
+ *    before any stream capture begins.
+ *  - All calls on a device share the one array, which keeps the previous call's contents.
+ *    Nothing in it needs clearing between calls (each call overwrites all it reads), but two
+ *    calls that overlap on the GPU (different streams, or concurrent graph branches) race
+ *    on it: serialise them. */
+size_t oq_static_scratch_bytes(void);
+int oq_linear_forward_static(void *out, const void *x, int dtype, int64_t rows,
+                             int64_t in_features, int64_t out_features, const uint8_t *packed,
+                             int64_t packed_bytes, int weight_bits, const void *row_norms_bf16,
+                             const float *weight_centroids, const void *bias, int bias_dtype,
+                             const int32_t *perm, const int8_t *signs, int64_t block,
+                             const float *act_boundaries, const float *act_centroids,
+                             int act_bits, float eps, int weight_mode, int kernel, void *stream);
+
 /* ---- device status ------------------------------------------------------------------- */
 
 /* Every wait inside the tcgen05 kernel (on an mbarrier) is bounded; a wait that gives up

@@ -44,6 +44,10 @@ _SIGNATURES = {
     "oq_linear_forward": (_int, [_vp, _vp, _int, _i64, _i64, _i64, _vp, _i64, _int, _vp, _vp,
                                  _vp, _int, _vp, _vp, _i64, _vp, _vp, _int, _f32, _int, _int,
                                  _vp, _sz, _vp]),
+    "oq_linear_forward_static": (_int, [_vp, _vp, _int, _i64, _i64, _i64, _vp, _i64, _int, _vp, _vp,
+                                        _vp, _int, _vp, _vp, _i64, _vp, _vp, _int, _f32, _int, _int,
+                                        _vp]),
+    "oq_static_scratch_bytes": (_sz, []),
     "oq_linear_workspace_bytes": (_sz, [_i64, _i64, _i64, _int, _int, _int, _int]),
     "oq_gemm_device_status": (_int, [ctypes.POINTER(ctypes.c_int)]),
     "oq_gemm_clear_device_status": (_int, []),
