@@ -48,7 +48,12 @@ WORKLOADS = {
 
 # DRAM bytes (read + write) per launch of the dominant kernel from an ncu capture, keyed by
 # workload; filled from the summaries under profiles/ (None until captured).
-NCU_TRAFFIC_BYTES = {"dit_block": None, "video_dit": None, "vit_decode": None}
+NCU_TRAFFIC_BYTES = {
+    # profiles/gemm_w4_tcgen05_dit_block_traffic.md: mean over the four projections
+    "dit_block": 122.2e6,
+    "video_dit": None,
+    "vit_decode": None,
+}
 
 CPU_SAMPLE_ROWS = 512
 
