@@ -348,13 +348,13 @@ def main():
             module._activation_codebook_centroids, module._activation_codebook_boundaries,
             eps=module.activation_eps, block_size=module.rotation.block_size)
         if small:
-            prepared.append((xq, None))
+            prepared.append((xq, None, None))
         else:
-            prepared.append(native.rows_to_f16_operand(xq))
+            prepared.append(native.rows_to_f16_operand(xq, module._weight_codebook_centroids))
     torch.cuda.synchronize()
     events = []
     for it in range(args.steps + 2):
-        for (name, k, n, gather, module), (operand, scale) in zip(layers, prepared):
+        for (name, k, n, gather, module), (operand, scale, table) in zip(layers, prepared):
             e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             e0.record()
             if small:
@@ -365,7 +365,8 @@ def main():
             else:
                 native.gemm_tcgen05_f16(operand, scale, module.packed_weight_indices,
                                         module.row_norms, module._weight_codebook_centroids,
-                                        out_features=module.out_features, bias=module.bias)
+                                        out_features=module.out_features, bias=module.bias,
+                                        table_scale=table)
             e1.record()
             if it >= 2:
                 events.append((e0, e1))

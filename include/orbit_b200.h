@@ -140,25 +140,31 @@ int oq_matmul_packed_weight(void *out, const void *x, int dtype, int64_t rows,
 size_t oq_matmul_workspace_bytes(int64_t rows, int64_t in_features, int64_t out_features,
                                  int bits, int dtype, int weight_mode, int kernel);
 
-/* 1 when the tcgen05/TMEM kernel can run this problem (bf16, W4, in_features % 64 == 0,
- * 16-byte aligned rows), else 0. */
+/* 1 when the tcgen05/TMEM kernel can run this problem (bf16 activations, 2/3/4/6/8-bit
+ * weights, in_features % 64 == 0, centroid weight mode), else 0. */
 int oq_gemm_tcgen05_supported(int64_t rows, int64_t in_features, int64_t out_features,
                               int bits, int dtype, int weight_mode);
 
 /* The tcgen05 kernel alone, on an activation operand that is already in its f16 form:
  * x_f16[m,k] = f16(x[m,k] / row_scale[m]) with row_scale[m] an exact power of two (what
  * oq_linear_forward's prologue writes into the workspace, and what oq_matmul_packed_weight
- * derives from a caller-supplied x).  out is bf16.  Same reference counterpart as
- * oq_matmul_packed_weight; exposed so that tests and the benchmark can time and check the
- * GEMM kernel in isolation.  Requires oq_gemm_tcgen05_supported(...) == 1. */
-int oq_gemm_tcgen05_f16(void *out, const void *x_f16, const float *row_scale, int64_t rows,
-                        int64_t in_features, int64_t out_features, const uint8_t *packed,
-                        int64_t packed_bytes, const void *row_norms_bf16, const float *centroids,
-                        const void *bias, int bias_dtype, void *stream);
+ * derives from a caller-supplied x).  table_scale points at the scale of the kernel's f16
+ * weight table f16(centroid * scale), chosen by oq_rows_to_f16_operand (NULL: 2^8).
+ * out is bf16.  Same reference counterpart as oq_matmul_packed_weight; exposed so that
+ * tests and the benchmark can time and check the GEMM kernel in isolation.  Requires
+ * oq_gemm_tcgen05_supported(...) == 1. */
+int oq_gemm_tcgen05_f16(void *out, const void *x_f16, const float *row_scale,
+                        const float *table_scale, int64_t rows, int64_t in_features,
+                        int64_t out_features, const uint8_t *packed, int64_t packed_bytes, int bits,
+                        const void *row_norms_bf16, const float *centroids, const void *bias,
+                        int bias_dtype, void *stream);
 
-/* x (bf16 or f16, [rows, dim]) -> the f16 operand and per-token factors used above. */
+/* x (bf16 or f16, [rows, dim]) -> the f16 operand and per-token factors used above.  When
+ * table_scale is not NULL the kernel also searches the weight-table scale for the codebook
+ * `centroids` (f32[2^bits]) and writes it there (one float). */
 int oq_rows_to_f16_operand(const void *x, int dtype, int64_t rows, int64_t dim, void *x_f16,
-                           float *row_scale, void *stream);
+                           float *row_scale, const float *centroids, int bits,
+                           float *table_scale, void *stream);
 
 /* ---- the whole quantized-linear forward --------------------------------------------- */
 

@@ -20,6 +20,7 @@ int launch_rotate_quantize(const void *x, int x_dtype, int64_t rows, int64_t dim
                            const int32_t *perm, const int8_t *signs, int64_t block,
                            const float *boundaries, const float *centroids, int bits, float eps,
                            void *x_q, uint8_t *codes, float *norms, float *f16_row_scale,
+                           const float *w_centroids, int w_bits, float *table_scale_out,
                            cudaStream_t stream);
 int launch_tiled_matmul(void *out, const void *x, int dtype, int64_t rows, int64_t in_features,
                         int64_t out_features, const uint8_t *packed, int bits,
@@ -41,9 +42,10 @@ int launch_dequantize(const uint8_t *packed, int bits, int64_t out_features, int
 bool tcgen05_gemm_supported(int64_t rows, int64_t in_features, int64_t out_features, int bits,
                             int dtype, int weight_mode);
 int launch_rows_to_f16(const void *x, int dtype, int64_t rows, int64_t dim, void *out_f16,
-                       float *row_scale, cudaStream_t stream);
-int launch_tcgen05_gemm(void *out, const void *x_f16, const float *row_scale, int64_t rows,
-                        int64_t in_features, int64_t out_features, const uint8_t *packed,
+                       float *row_scale, const float *centroids, int bits, float *table_scale_out,
+                       cudaStream_t stream);
+int launch_tcgen05_gemm(void *out, const void *x_f16, const float *row_scale,
+                        const float *table_scale, int64_t rows, int64_t in_features, int64_t out_features, const uint8_t *packed, int bits,
                         const void *row_norms_bf16, const float *centroids, const void *bias,
                         int bias_dtype, cudaStream_t stream);
 int read_gemm_status(int *status);
@@ -160,7 +162,8 @@ int oq_quantize_activations(const void *x, int x_dtype, int64_t rows, int64_t di
     return rc;
   }
   return launch_rotate_quantize(x, x_dtype, rows, dim, perm, signs, block, boundaries, centroids,
-                                bits, eps, x_q, codes, norms, nullptr, static_cast<cudaStream_t>(stream));
+                                bits, eps, x_q, codes, norms, nullptr, nullptr, 0, nullptr,
+                                static_cast<cudaStream_t>(stream));
 }
 
 int oq_gemm_tcgen05_supported(int64_t rows, int64_t in_features, int64_t out_features, int bits,
@@ -180,7 +183,7 @@ size_t oq_matmul_workspace_bytes(int64_t rows, int64_t in_features, int64_t out_
   if (choose_kernel(kernel, rows, in_features, out_features, bits, dtype, mode) != OQ_KERNEL_TCGEN05) {
     return 0;
   }
-  return f16_operand_bytes(rows, in_features) + align_up(static_cast<size_t>(rows) * 4, 256);
+  return f16_operand_bytes(rows, in_features) + align_up(static_cast<size_t>(rows + 1) * 4, 256);
 }
 
 int oq_matmul_packed_weight(void *out, const void *x, int dtype, int64_t rows, int64_t in_features,
@@ -217,8 +220,8 @@ int oq_matmul_packed_weight(void *out, const void *x, int dtype, int64_t rows, i
     case OQ_KERNEL_TCGEN05:
       if (!tcgen05_gemm_supported(rows, in_features, out_features, bits, dtype, mode)) {
         return fail(OQ_ERR_UNSUPPORTED,
-                    "the tcgen05 kernel takes bf16 activations, 4-bit weights, in_features %% 64 == 0 "
-                    "and the centroid weight mode");
+                    "the tcgen05 kernel takes bf16 activations, 2/3/4/6/8-bit weights, "
+                    "in_features %% 64 == 0 and the centroid weight mode");
       }
       {
         const size_t need = oq_matmul_workspace_bytes(rows, in_features, out_features, bits, dtype,
@@ -229,11 +232,14 @@ int oq_matmul_packed_weight(void *out, const void *x, int dtype, int64_t rows, i
         OQ_CHECK_ARG(aligned16(workspace), "workspace must be 16-byte aligned");
         float *row_scale = reinterpret_cast<float *>(static_cast<unsigned char *>(workspace) +
                                                      f16_operand_bytes(rows, in_features));
-        if (int rc = launch_rows_to_f16(x, dtype, rows, in_features, workspace, row_scale, s)) {
+        float *table_scale = row_scale + rows;  // one float after the per-token factors
+        if (int rc = launch_rows_to_f16(x, dtype, rows, in_features, workspace, row_scale, centroids,
+                                        bits, table_scale, s)) {
           return rc;
         }
-        return launch_tcgen05_gemm(out, workspace, row_scale, rows, in_features, out_features, packed,
-                                   row_norms_bf16, centroids, bias, bias_dtype, s);
+        return launch_tcgen05_gemm(out, workspace, row_scale, table_scale, rows, in_features,
+                                   out_features, packed, bits, row_norms_bf16, centroids, bias,
+                                   bias_dtype, s);
       }
     default:
       return launch_tiled_matmul(out, x, dtype, rows, in_features, out_features, packed, bits,
@@ -241,30 +247,34 @@ int oq_matmul_packed_weight(void *out, const void *x, int dtype, int64_t rows, i
   }
 }
 
-int oq_gemm_tcgen05_f16(void *out, const void *x_f16, const float *row_scale, int64_t rows,
+int oq_gemm_tcgen05_f16(void *out, const void *x_f16, const float *row_scale,
+                        const float *table_scale, int64_t rows,
                         int64_t in_features, int64_t out_features, const uint8_t *packed,
-                        int64_t packed_bytes, const void *row_norms_bf16, const float *centroids,
-                        const void *bias, int bias_dtype, void *stream) {
+                        int64_t packed_bytes, int bits, const void *row_norms_bf16,
+                        const float *centroids, const void *bias, int bias_dtype, void *stream) {
   OQ_CHECK_ARG(rows >= 0 && in_features > 0 && out_features >= 0, "negative or empty shape");
+  OQ_CHECK_ARG(bits >= 1 && bits <= 8, "bits must be in [1, 8]");
   OQ_CHECK_ARG(bias == nullptr || valid_dtype(bias_dtype), "bias must be float32, float16, or bfloat16");
-  OQ_CHECK_ARG(packed_bytes >= (out_features * in_features * 4 + 7) / 8, "packed weights are too short");
+  OQ_CHECK_ARG(packed_bytes >= (out_features * in_features * bits + 7) / 8, "packed weights are too short");
   if (rows == 0 || out_features == 0) {
     return OQ_OK;
   }
   OQ_CHECK_ARG(out && x_f16 && row_scale && packed && row_norms_bf16 && centroids, "null device pointer");
-  if (!tcgen05_gemm_supported(rows, in_features, out_features, 4, OQ_DTYPE_BF16, OQ_WEIGHT_CENTROID)) {
-    return fail(OQ_ERR_UNSUPPORTED, "the tcgen05 kernel needs in_features %% 64 == 0");
+  if (!tcgen05_gemm_supported(rows, in_features, out_features, bits, OQ_DTYPE_BF16, OQ_WEIGHT_CENTROID)) {
+    return fail(OQ_ERR_UNSUPPORTED, "the tcgen05 kernel needs 2/3/4/6/8-bit weights and in_features %% 64 == 0");
   }
   if (int rc = check_device()) {
     return rc;
   }
-  return launch_tcgen05_gemm(out, x_f16, row_scale, rows, in_features, out_features, packed,
+  return launch_tcgen05_gemm(out, x_f16, row_scale, table_scale, rows, in_features, out_features,
+                             packed, bits,
                              row_norms_bf16, centroids, bias, bias_dtype,
                              static_cast<cudaStream_t>(stream));
 }
 
 int oq_rows_to_f16_operand(const void *x, int dtype, int64_t rows, int64_t dim, void *x_f16,
-                           float *row_scale, void *stream) {
+                           float *row_scale, const float *centroids, int bits,
+                           float *table_scale, void *stream) {
   OQ_CHECK_ARG(rows >= 0 && dim > 0, "negative or empty shape");
   if (rows == 0) {
     return OQ_OK;
@@ -273,7 +283,8 @@ int oq_rows_to_f16_operand(const void *x, int dtype, int64_t rows, int64_t dim, 
   if (int rc = check_device()) {
     return rc;
   }
-  return launch_rows_to_f16(x, dtype, rows, dim, x_f16, row_scale, static_cast<cudaStream_t>(stream));
+  return launch_rows_to_f16(x, dtype, rows, dim, x_f16, row_scale, centroids, bits, table_scale,
+                            static_cast<cudaStream_t>(stream));
 }
 
 size_t oq_linear_workspace_bytes(int64_t rows, int64_t in_features, int64_t out_features,
@@ -285,7 +296,7 @@ size_t oq_linear_workspace_bytes(int64_t rows, int64_t in_features, int64_t out_
   if (choose_kernel(kernel, rows, in_features, out_features, weight_bits, dtype, mode) ==
       OQ_KERNEL_TCGEN05) {
     // the prologue writes the f16 operand and its per-token factors straight into it
-    return f16_operand_bytes(rows, in_features) + align_up(static_cast<size_t>(rows) * 4, 256);
+    return f16_operand_bytes(rows, in_features) + align_up(static_cast<size_t>(rows + 1) * 4, 256);
   }
   return align_up(static_cast<size_t>(rows) * in_features * dtype_size(dtype), 256);
 }
@@ -327,17 +338,20 @@ int oq_linear_forward(void *out, const void *x, int dtype, int64_t rows, int64_t
     OQ_CHECK_ARG(out && packed && row_norms_bf16 && weight_centroids, "null device pointer");
     float *row_scale = reinterpret_cast<float *>(static_cast<unsigned char *>(workspace) +
                                                  f16_operand_bytes(rows, in_features));
+    float *table_scale = row_scale + rows;  // one float after the per-token factors
     if (int rc = launch_rotate_quantize(x, dtype, rows, in_features, perm, signs, block,
                                         act_boundaries, act_centroids, act_bits, eps, workspace,
-                                        nullptr, nullptr, row_scale, s)) {
+                                        nullptr, nullptr, row_scale, weight_centroids, weight_bits,
+                                        table_scale, s)) {
       return rc;
     }
-    return launch_tcgen05_gemm(out, workspace, row_scale, rows, in_features, out_features, packed,
-                               row_norms_bf16, weight_centroids, bias, bias_dtype, s);
+    return launch_tcgen05_gemm(out, workspace, row_scale, table_scale, rows, in_features,
+                               out_features, packed, weight_bits, row_norms_bf16, weight_centroids,
+                               bias, bias_dtype, s);
   }
   if (int rc = launch_rotate_quantize(x, dtype, rows, in_features, perm, signs, block, act_boundaries,
                                       act_centroids, act_bits, eps, workspace, nullptr, nullptr,
-                                      nullptr, s)) {
+                                      nullptr, nullptr, 0, nullptr, s)) {
     return rc;
   }
   return oq_matmul_packed_weight(out, workspace, dtype, rows, in_features, out_features, packed,

@@ -37,6 +37,7 @@
 #include <mutex>
 
 #include "common.cuh"
+#include "table_scale.cuh"
 
 namespace oq {
 
@@ -49,17 +50,28 @@ constexpr int kBK = 64;
 constexpr int kThreads = 320;
 constexpr int kProducerWarp = 8;
 constexpr int kMmaWarp = 9;
-constexpr float kCentroidScale = 256.0f;  // f16 operand = centroid * 2^8 (exact scaling)
+constexpr float kCentroidScale = kTableScaleBase;  // table scale when none was searched
 constexpr uint32_t kSpinLimit = 1u << 22;
 
-template <int BN>
+template <int BN, int BITS>
 struct Tile {
-  static constexpr int kStages = BN == 128 ? 4 : 3;
+
   static constexpr int kABytes = kBM * kBK * 2;        // 32 KB
   static constexpr int kBBytes = BN * kBK * 2;         // expanded f16 tile
-  static constexpr int kPBytes = BN * (kBK / 2);       // packed 4-bit tile
-  static constexpr int kStageBytes = kABytes + kBBytes + kPBytes;
-  static constexpr int kHeaderBytes = 256 /*barriers*/ + 2 * BN * 4 /*scale,bias*/;
+  static constexpr int kRowBytes = kBK * BITS / 8;     // packed bytes of one weight row per k step
+  static constexpr int kPBytes = BN * kRowBytes;       // packed tile
+  // 3-bit rows advance by 24 bytes per k step, which no bulk tensor copy can address
+  // (16-byte rule); those tiles are read from global memory by the expanders instead.
+  static constexpr bool kPackedByTma = BITS != 3;
+  static constexpr int kLutBytes = BITS == 6 ? 64 * 32 * 2 : (BITS == 8 ? 256 * 8 * 2 : 0);
+  // every stage starts 1024-byte aligned (the 128-byte swizzle pattern repeats every 1024 bytes)
+  static constexpr int kStageBytes = (kABytes + kBBytes + kPBytes + 1023) / 1024 * 1024;
+  static constexpr int kHeaderBytes =
+      256 /*barriers*/ + 2 * BN * 4 /*scale,bias*/ + 256 * 4 /*centroids*/ + kLutBytes;
+  // as many stages as fit in the 227 KB a CTA may use, at most 4
+  static constexpr int kFit = (232448 - kHeaderBytes - 1024) / kStageBytes;
+  static constexpr int kStages = kFit > 4 ? 4 : kFit;
+  static_assert(kStages >= 2, "tile does not fit in shared memory");
   static constexpr int kSmemBytes = kHeaderBytes + 1024 /*alignment slack*/ + kStages * kStageBytes;
   static constexpr int kTmemCols = BN == 128 ? 256 : 512;  // power of two >= 2 * BN
   static constexpr int kExpanderWarps = BN == 128 ? 8 : BN / 32;  // warps that own weight rows
@@ -67,7 +79,9 @@ struct Tile {
 
 struct GemmParams {
   void *out;
+  const uint8_t *packed;   // the bit stream (read directly only by the 3-bit expanders)
   const float *row_scale;  // per token: factor the f16 activations were divided by
+  const float *table_scale;  // scale of the f16 weight table (NULL: 2^8)
   const __nv_bfloat16 *row_norms;
   const float *centroids;
   const void *bias;
@@ -221,12 +235,25 @@ __device__ __forceinline__ float load_bias(const void *bias, int dtype, int64_t 
   }
 }
 
-// Eight 4-bit indices (one 32-bit word of the stream, lowest k in the low nibble) -> eight
-// f16 table entries, in k order.  prmt picks one of 8 bytes with a 3-bit selector, so the
-// 16-entry table is looked up as two 8-entry halves and bit 3 of the index chooses between
-// them through a byte mask (itself a prmt of the constant 0x0000ff00).
-__device__ __forceinline__ void decode8(uint32_t w, const uint32_t (&tab_hi)[4],
-                                        const uint32_t (&tab_lo)[4], uint4 &out) {
+// ---- index -> f16 centroid decode ---------------------------------------------------------
+//
+// Every routine turns the 8*BITS bits of eight consecutive indices (lowest k first, held in
+// `lo` / `hi`) into eight f16 table entries in k order.  Tables of up to 16 entries live in
+// registers as separate high-byte / low-byte vectors and are read with prmt (byte permute,
+// 3-bit selectors); 64- and 256-entry tables live in shared memory.
+
+struct RegTable {
+  uint32_t hi[4];  // high bytes of entries 4q .. 4q+3
+  uint32_t lo[4];
+};
+
+__device__ __forceinline__ void pair_up(uint32_t lo, uint32_t hi, uint32_t &r0, uint32_t &r1) {
+  r0 = __byte_perm(lo, hi, 0x5140u);  // entries 0, 1 as two f16
+  r1 = __byte_perm(lo, hi, 0x7362u);  // entries 2, 3
+}
+
+// 4-bit: two 8-entry halves, bit 3 of the index picks the half through a byte mask.
+__device__ __forceinline__ void decode8_w4(uint32_t w, const RegTable &t, uint4 &out) {
   const uint32_t low3 = w & 0x77777777u;
   const uint32_t bit3 = (w >> 3) & 0x11111111u;
   uint32_t r[4];
@@ -234,23 +261,76 @@ __device__ __forceinline__ void decode8(uint32_t w, const uint32_t (&tab_hi)[4],
   for (int h = 0; h < 2; ++h) {
     const uint32_t sel = low3 >> (16 * h);
     const uint32_t mask = __byte_perm(0x0000ff00u, 0u, bit3 >> (16 * h));
-    const uint32_t hx = __byte_perm(tab_hi[0], tab_hi[1], sel);
-    const uint32_t hy = __byte_perm(tab_hi[2], tab_hi[3], sel);
-    const uint32_t lx = __byte_perm(tab_lo[0], tab_lo[1], sel);
-    const uint32_t ly = __byte_perm(tab_lo[2], tab_lo[3], sel);
-    const uint32_t hi = (hx & ~mask) | (hy & mask);
-    const uint32_t lo = (lx & ~mask) | (ly & mask);
-    r[2 * h] = __byte_perm(lo, hi, 0x5140u);
-    r[2 * h + 1] = __byte_perm(lo, hi, 0x7362u);
+    const uint32_t hx = __byte_perm(t.hi[0], t.hi[1], sel);
+    const uint32_t hy = __byte_perm(t.hi[2], t.hi[3], sel);
+    const uint32_t lx = __byte_perm(t.lo[0], t.lo[1], sel);
+    const uint32_t ly = __byte_perm(t.lo[2], t.lo[3], sel);
+    pair_up((lx & ~mask) | (ly & mask), (hx & ~mask) | (hy & mask), r[2 * h], r[2 * h + 1]);
   }
   out = make_uint4(r[0], r[1], r[2], r[3]);
 }
 
-template <int BN>
+// 3-bit: 24 bits; spread each 3-bit field to its own selector nibble.
+__device__ __forceinline__ void decode8_w3(uint32_t w, const RegTable &t, uint4 &out) {
+  uint32_t r[4];
+#pragma unroll
+  for (int h = 0; h < 2; ++h) {
+    const uint32_t v = (w >> (12 * h)) & 0xfffu;                      // fields f0..f3
+    const uint32_t a = (v & 0x03fu) | ((v & 0xfc0u) << 2);            // f0 f1 | f2 f3 per byte
+    const uint32_t sel = (a & 0x0707u) | ((a & 0x3838u) << 1);        // one field per nibble
+    pair_up(__byte_perm(t.lo[0], t.lo[1], sel), __byte_perm(t.hi[0], t.hi[1], sel), r[2 * h],
+            r[2 * h + 1]);
+  }
+  out = make_uint4(r[0], r[1], r[2], r[3]);
+}
+
+// 2-bit: 16 bits; spread each 2-bit field to its own selector nibble.
+__device__ __forceinline__ void decode8_w2(uint32_t w, const RegTable &t, uint4 &out) {
+  uint32_t r[4];
+#pragma unroll
+  for (int h = 0; h < 2; ++h) {
+    const uint32_t v = (w >> (8 * h)) & 0xffu;
+    const uint32_t a = (v | (v << 4)) & 0x0f0fu;
+    const uint32_t sel = (a | (a << 2)) & 0x3333u;
+    pair_up(__byte_perm(t.lo[0], 0u, sel), __byte_perm(t.hi[0], 0u, sel), r[2 * h], r[2 * h + 1]);
+  }
+  out = make_uint4(r[0], r[1], r[2], r[3]);
+}
+
+// 6- and 8-bit: one shared-memory read per index.  `lut` already points at this lane's copy;
+// entry e sits kStride halfwords further.
+template <int BITS, int kStride>
+__device__ __forceinline__ void decode8_lut(uint32_t lo, uint32_t hi, const uint16_t *lut, uint4 &out) {
+  const uint64_t v = (static_cast<uint64_t>(hi) << 32) | lo;
+  uint32_t r[4];
+#pragma unroll
+  for (int e = 0; e < 8; e += 2) {
+    const uint32_t i0 = static_cast<uint32_t>(v >> (BITS * e)) & ((1u << BITS) - 1u);
+    const uint32_t i1 = static_cast<uint32_t>(v >> (BITS * (e + 1))) & ((1u << BITS) - 1u);
+    r[e >> 1] = static_cast<uint32_t>(lut[i0 * kStride]) | (static_cast<uint32_t>(lut[i1 * kStride]) << 16);
+  }
+  out = make_uint4(r[0], r[1], r[2], r[3]);
+}
+
+// Bits [offset, offset + 8*BITS) of a word array, offset a compile-time constant after unrolling.
+template <int BITS, int NWORDS>
+__device__ __forceinline__ void group_bits(const uint32_t (&words)[NWORDS], int group, uint32_t &lo,
+                                           uint32_t &hi) {
+  const int offset = 8 * BITS * group;
+  const int w = offset >> 5;
+  const int sh = offset & 31;
+  const uint32_t w0 = words[w];
+  const uint32_t w1 = w + 1 < NWORDS ? words[w + 1] : 0u;
+  const uint32_t w2 = w + 2 < NWORDS ? words[w + 2] : 0u;
+  lo = __funnelshift_r(w0, w1, sh);
+  hi = BITS > 4 ? __funnelshift_r(w1, w2, sh) : 0u;
+}
+
+template <int BN, int BITS>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_w4_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
                        const __grid_constant__ CUtensorMap map_p, const GemmParams p) {
-  using T = Tile<BN>;
+  using T = Tile<BN, BITS>;
   extern __shared__ __align__(16) unsigned char smem_raw[];
   // header: barriers | scale[BN] | bias[BN]
   uint64_t *bars = reinterpret_cast<uint64_t *>(smem_raw);
@@ -258,6 +338,8 @@ gemm_w4_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
   volatile int *s_abort = reinterpret_cast<volatile int *>(smem_raw + 200);
   float *s_scale = reinterpret_cast<float *>(smem_raw + 256);
   float *s_bias = s_scale + BN;
+  float *s_cent = s_bias + BN;                                   // [256] codebook
+  uint16_t *s_lut = reinterpret_cast<uint16_t *>(s_cent + 256);  // 6- and 8-bit tables only
   const uint32_t header_end = smem_u32(smem_raw) + T::kHeaderBytes;
   const uint32_t stage_base = (header_end + 1023u) & ~1023u;
   unsigned char *stage_ptr = smem_raw + (stage_base - smem_u32(smem_raw));
@@ -296,10 +378,25 @@ gemm_w4_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
     asm volatile("prefetch.tensormap [%0];" ::"l"(&map_a) : "memory");
     asm volatile("prefetch.tensormap [%0];" ::"l"(&map_p) : "memory");
   }
+  for (int i = threadIdx.x; i < (1 << BITS); i += kThreads) {
+    s_cent[i] = p.centroids[i];
+  }
+  __syncthreads();
+  // chosen by the kernel that ran just before this one (table_scale.cuh); 2^8 without it
+  const float table_scale = p.table_scale != nullptr ? __ldg(p.table_scale) : kCentroidScale;
+  if (BITS == 6) {  // [entry][32 lane copies]
+    for (int i = threadIdx.x; i < 64 * 32; i += kThreads) {
+      s_lut[i] = __half_as_ushort(__float2half_rn(s_cent[i >> 5] * table_scale));
+    }
+  } else if (BITS == 8) {  // [entry][8 copies]
+    for (int i = threadIdx.x; i < 256 * 8; i += kThreads) {
+      s_lut[i] = __half_as_ushort(__float2half_rn(s_cent[i >> 3] * table_scale));
+    }
+  }
   for (int i = threadIdx.x; i < BN; i += kThreads) {
     const int64_t n = n0 + i;
     const bool ok = n < p.out_features;
-    s_scale[i] = ok ? __bfloat162float(p.row_norms[n]) * (1.0f / kCentroidScale) : 0.0f;
+    s_scale[i] = ok ? __fdiv_rn(__bfloat162float(p.row_norms[n]), table_scale) : 0.0f;
     s_bias[i] = (ok && p.bias_dtype >= 0) ? load_bias(p.bias, p.bias_dtype, n) : 0.0f;
   }
   tc_fence_before();
@@ -316,9 +413,11 @@ gemm_w4_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
         if (!mbar_wait(empty_bar(s), phase ^ 1u, s_abort, 1)) {
           break;
         }
-        mbar_arrive_expect_tx(full_bar(s), T::kABytes + T::kPBytes);
+        mbar_arrive_expect_tx(full_bar(s), T::kABytes + (T::kPackedByTma ? T::kPBytes : 0));
         tma_load_2d(a_addr(s), &map_a, full_bar(s), it * kBK, static_cast<int>(m0));
-        tma_load_2d(smem_u32(p_ptr(s)), &map_p, full_bar(s), it * (kBK / 2), static_cast<int>(n0));
+        if (T::kPackedByTma) {
+          tma_load_2d(smem_u32(p_ptr(s)), &map_p, full_bar(s), it * T::kRowBytes, static_cast<int>(n0));
+        }
         issued = it + 1;
       }
       if (*s_abort != 0) {
@@ -362,57 +461,110 @@ gemm_w4_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
   } else {
     // ---- expanders ----
     constexpr int kThreadsPerRow = BN == 128 ? 2 : 1;  // BN=192 leaves warps 6 and 7 without rows
-    constexpr int kBytesPerThread = 32 / kThreadsPerRow;
-    constexpr int kChunksPerThread = kBytesPerThread / 4;
+    constexpr int kBytesPerThread = T::kRowBytes / kThreadsPerRow;
+    constexpr int kWords = kBytesPerThread / 4;
+    constexpr int kGroups = (kBK / 8) / kThreadsPerRow;   // 16-byte output chunks per thread
     const int et = threadIdx.x;  // 0..255
     const int row = et / kThreadsPerRow;
     const int part = et % kThreadsPerRow;
-    // Register table: entry i = f16(centroid[i] * 2^8); hi/lo bytes of entries 4q..4q+3.
-    uint32_t tab_hi[4];
-    uint32_t tab_lo[4];
+    // Register table (2-, 3-, 4-bit): entry i = f16(centroid[i] * 2^8).
+    RegTable table;
 #pragma unroll
     for (int q = 0; q < 4; ++q) {
       uint32_t hi = 0;
       uint32_t lo = 0;
 #pragma unroll
       for (int e = 0; e < 4; ++e) {
-        const uint32_t bits = __half_as_ushort(__float2half_rn(p.centroids[4 * q + e] * kCentroidScale));
+        const int idx = 4 * q + e;
+        const float c = (BITS <= 4 && idx < (1 << BITS)) ? s_cent[idx] : 0.0f;
+        const uint32_t bits = __half_as_ushort(__float2half_rn(c * table_scale));
         hi |= (bits >> 8) << (8 * e);
         lo |= (bits & 0xffu) << (8 * e);
       }
-      tab_hi[q] = hi;
-      tab_lo[q] = lo;
+      table.hi[q] = hi;
+      table.lo[q] = lo;
     }
+    const uint16_t *lane_lut = s_lut + (BITS == 6 ? lane : (lane & 7));
     const uint32_t row_off = (row >> 3) * 1024 + (row & 7) * 128;
+    // 3-bit rows come straight from global memory (8-byte loads, one k step ahead).
+    const int64_t n_global = n0 + row;
+    const bool row_valid = n_global < p.out_features;
+    const uint8_t *grow = p.packed + n_global * (static_cast<int64_t>(p.k_iters) * T::kRowBytes) +
+                          part * kBytesPerThread;
+    uint32_t words[kWords];
+    auto load_global = [&](int it, uint32_t (&dst)[kWords]) {
+#pragma unroll
+      for (int q = 0; q < kWords; ++q) {
+        dst[q] = (row_valid && it < p.k_iters)
+                     ? __ldg(reinterpret_cast<const uint32_t *>(grow + static_cast<int64_t>(it) * T::kRowBytes) + q)
+                     : 0u;
+      }
+    };
     bool ok = true;
     const int expand_iters = warp < T::kExpanderWarps ? p.k_iters : 0;
+    if (!T::kPackedByTma && expand_iters > 0) {
+      load_global(0, words);
+    }
     for (int it = 0; it < expand_iters; ++it) {
       const int s = it % T::kStages;
       const uint32_t phase = (it / T::kStages) & 1u;
+      uint32_t next_words[kWords];
+      if (!T::kPackedByTma) {
+        load_global(it + 1, next_words);
+      }
       if (!mbar_wait(full_bar(s), phase, s_abort, 4)) {
         ok = false;
         break;
       }
-      const uint4 *src = reinterpret_cast<const uint4 *>(p_ptr(s) + row * 32 + part * kBytesPerThread);
-      uint32_t words[kChunksPerThread];
+      if (T::kPackedByTma) {
+        const unsigned char *src = p_ptr(s) + row * T::kRowBytes + part * kBytesPerThread;
+        if (kBytesPerThread % 16 == 0) {
 #pragma unroll
-      for (int q = 0; q < kChunksPerThread / 4; ++q) {
-        const uint4 v = src[q];
-        words[4 * q + 0] = v.x;
-        words[4 * q + 1] = v.y;
-        words[4 * q + 2] = v.z;
-        words[4 * q + 3] = v.w;
+          for (int q = 0; q < kWords / 4; ++q) {
+            const uint4 v = reinterpret_cast<const uint4 *>(src)[q];
+            words[4 * q + 0] = v.x;
+            words[4 * q + 1] = v.y;
+            words[4 * q + 2] = v.z;
+            words[4 * q + 3] = v.w;
+          }
+        } else {
+#pragma unroll
+          for (int q = 0; q < kWords / 2; ++q) {
+            const uint2 v = reinterpret_cast<const uint2 *>(src)[q];
+            words[2 * q] = v.x;
+            words[2 * q + 1] = v.y;
+          }
+        }
       }
       const uint32_t dst_row = b_addr(s) + row_off;
 #pragma unroll
-      for (int c = 0; c < kChunksPerThread; ++c) {
+      for (int c = 0; c < kGroups; ++c) {
+        uint32_t lo;
+        uint32_t hi;
+        group_bits<BITS, kWords>(words, c, lo, hi);
         uint4 o;
-        decode8(words[c], tab_hi, tab_lo, o);
-        const int chunk = part * kChunksPerThread + c;
+        if (BITS == 4) {
+          decode8_w4(lo, table, o);
+        } else if (BITS == 3) {
+          decode8_w3(lo, table, o);
+        } else if (BITS == 2) {
+          decode8_w2(lo, table, o);
+        } else if (BITS == 6) {
+          decode8_lut<6, 32>(lo, hi, lane_lut, o);
+        } else {
+          decode8_lut<8, 8>(lo, hi, lane_lut, o);
+        }
+        const int chunk = part * kGroups + c;
         const uint32_t dst = dst_row + (((chunk ^ (row & 7)) & 7) << 4);
         asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(dst), "r"(o.x), "r"(o.y),
                      "r"(o.z), "r"(o.w)
                      : "memory");
+      }
+      if (!T::kPackedByTma) {
+#pragma unroll
+        for (int q = 0; q < kWords; ++q) {
+          words[q] = next_words[q];
+        }
       }
       fence_proxy_async_smem();
       __syncwarp();
@@ -480,7 +632,13 @@ gemm_w4_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
 // exact in f16 unless they lie more than 2^28 below the token's maximum.
 template <int DTYPE>
 __global__ void __launch_bounds__(256) rows_to_f16_kernel(const void *x, int64_t rows, int64_t dim,
-                                                          __half *out, float *row_scale) {
+                                                          __half *out, float *row_scale,
+                                                          const float *centroids, int bits,
+                                                          float *table_scale_out) {
+  __shared__ float s_search[272];
+  if (blockIdx.x == 0 && table_scale_out != nullptr) {
+    search_table_scale(centroids, bits, table_scale_out, s_search);
+  }
   const int lane = threadIdx.x & 31;
   const int64_t row = static_cast<int64_t>(blockIdx.x) * 8 + (threadIdx.x >> 5);
   if (row >= rows) {
@@ -558,18 +716,18 @@ EncodeTiledFn encode_tiled_fn() {
   return fn;
 }
 
-template <int BN>
+template <int BN, int BITS>
 int launch_bn(const CUtensorMap &map_a, const CUtensorMap &map_p, const GemmParams &p, int grid,
               cudaStream_t stream) {
   static std::once_flag once;
   static cudaError_t attr_status = cudaSuccess;
   std::call_once(once, [] {
-    attr_status = cudaFuncSetAttribute(gemm_w4_tcgen05_kernel<BN>,
+    attr_status = cudaFuncSetAttribute(gemm_w4_tcgen05_kernel<BN, BITS>,
                                        cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                       Tile<BN>::kSmemBytes);
+                                       Tile<BN, BITS>::kSmemBytes);
   });
   OQ_CHECK_CUDA(attr_status);
-  gemm_w4_tcgen05_kernel<BN><<<grid, kThreads, Tile<BN>::kSmemBytes, stream>>>(map_a, map_p, p);
+  gemm_w4_tcgen05_kernel<BN, BITS><<<grid, kThreads, Tile<BN, BITS>::kSmemBytes, stream>>>(map_a, map_p, p);
   OQ_CHECK_CUDA(cudaGetLastError());
   count_launch();
   return OQ_OK;
@@ -579,20 +737,24 @@ int launch_bn(const CUtensorMap &map_a, const CUtensorMap &map_p, const GemmPara
 
 bool tcgen05_gemm_supported(int64_t rows, int64_t in_features, int64_t out_features, int bits,
                             int dtype, int weight_mode) {
-  return rows > 0 && out_features > 0 && bits == 4 && dtype == OQ_DTYPE_BF16 &&
+  const bool bits_ok = bits == 2 || bits == 3 || bits == 4 || bits == 6 || bits == 8;
+  return rows > 0 && out_features > 0 && bits_ok && dtype == OQ_DTYPE_BF16 &&
          weight_mode != OQ_WEIGHT_BF16_SCALED && in_features >= kBK && in_features % kBK == 0 &&
          in_features <= (1 << 30) && rows < (1ll << 31) && out_features < (1ll << 31);
 }
 
 int launch_rows_to_f16(const void *x, int dtype, int64_t rows, int64_t dim, void *out_f16,
-                       float *row_scale, cudaStream_t stream) {
+                       float *row_scale, const float *centroids, int bits, float *table_scale_out,
+                       cudaStream_t stream) {
+  OQ_CHECK_ARG(table_scale_out == nullptr || (centroids != nullptr && bits >= 1 && bits <= 8),
+               "the table scale search needs the weight codebook");
   OQ_CHECK_ARG(dtype == OQ_DTYPE_BF16 || dtype == OQ_DTYPE_F16, "16-bit activations expected");
   OQ_CHECK_ARG(dim % 8 == 0 && aligned16(x) && aligned16(out_f16), "rows must be 16-byte aligned");
   const unsigned grid = static_cast<unsigned>((rows + 7) / 8);
   if (dtype == OQ_DTYPE_BF16) {
-    rows_to_f16_kernel<OQ_DTYPE_BF16><<<grid, 256, 0, stream>>>(x, rows, dim, static_cast<__half *>(out_f16), row_scale);
+    rows_to_f16_kernel<OQ_DTYPE_BF16><<<grid, 256, 0, stream>>>(x, rows, dim, static_cast<__half *>(out_f16), row_scale, centroids, bits, table_scale_out);
   } else {
-    rows_to_f16_kernel<OQ_DTYPE_F16><<<grid, 256, 0, stream>>>(x, rows, dim, static_cast<__half *>(out_f16), row_scale);
+    rows_to_f16_kernel<OQ_DTYPE_F16><<<grid, 256, 0, stream>>>(x, rows, dim, static_cast<__half *>(out_f16), row_scale, centroids, bits, table_scale_out);
   }
   OQ_CHECK_CUDA(cudaGetLastError());
   count_launch();
@@ -600,8 +762,18 @@ int launch_rows_to_f16(const void *x, int dtype, int64_t rows, int64_t dim, void
 }
 
 // `x` is the f16 operand [rows, in_features] and `row_scale` its per-token factor.
-int launch_tcgen05_gemm(void *out, const void *x, const float *row_scale, int64_t rows,
-                        int64_t in_features, int64_t out_features, const uint8_t *packed,
+template <int BITS>
+int launch_bits(int bn, const CUtensorMap &map_a, const CUtensorMap &map_p, const GemmParams &p,
+                int grid, cudaStream_t stream) {
+  switch (bn) {
+    case 256: return launch_bn<256, BITS>(map_a, map_p, p, grid, stream);
+    case 192: return launch_bn<192, BITS>(map_a, map_p, p, grid, stream);
+    default: return launch_bn<128, BITS>(map_a, map_p, p, grid, stream);
+  }
+}
+
+int launch_tcgen05_gemm(void *out, const void *x, const float *row_scale, const float *table_scale,
+                        int64_t rows, int64_t in_features, int64_t out_features, const uint8_t *packed, int bits,
                         const void *row_norms_bf16, const float *centroids, const void *bias,
                         int bias_dtype, cudaStream_t stream) {
   OQ_CHECK_ARG(aligned16(x) && aligned16(packed) && aligned16(out),
@@ -626,8 +798,9 @@ int launch_tcgen05_gemm(void *out, const void *x, const float *row_scale, int64_
                           static_cast<double>(((out_features + width - 1) / width) * width);
     return rate * useful * static_cast<double>(tiles) / static_cast<double>(waves * sm_count);
   };
-  int bn = 256;
-  double best = score(256, 1.0);
+  // 6- and 8-bit packed tiles leave room for only two 256-wide stages; start from 192 there.
+  int bn = bits >= 6 ? 192 : 256;
+  double best = bits >= 6 ? score(192, 0.93) : score(256, 1.0);
   if (score(192, 0.93) > best) {
     bn = 192;
     best = score(192, 0.93);
@@ -661,10 +834,15 @@ int launch_tcgen05_gemm(void *out, const void *x, const float *row_scale, int64_
     }
   }
   {
-    const cuuint64_t dims[2] = {static_cast<cuuint64_t>(in_features / 2),
-                                static_cast<cuuint64_t>(out_features)};
-    const cuuint64_t strides[1] = {static_cast<cuuint64_t>(in_features / 2)};
-    const cuuint32_t box[2] = {kBK / 2, static_cast<cuuint32_t>(bn)};
+    // 3-bit tiles are not fetched through this map (see Tile::kPackedByTma); it is still
+    // encoded, over a 16-byte-aligned view, so that every kernel takes the same arguments.
+    const int64_t row_bytes = in_features * bits / 8;
+    const bool by_tma = bits != 3;
+    const cuuint64_t dims[2] = {static_cast<cuuint64_t>(by_tma ? row_bytes : 16),
+                                static_cast<cuuint64_t>(by_tma ? out_features : 1)};
+    const cuuint64_t strides[1] = {static_cast<cuuint64_t>(by_tma ? row_bytes : 16)};
+    const cuuint32_t box[2] = {static_cast<cuuint32_t>(by_tma ? kBK * bits / 8 : 16),
+                               static_cast<cuuint32_t>(by_tma ? bn : 1)};
     const cuuint32_t elem[2] = {1, 1};
     const CUresult rc = encode(&map_p, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<uint8_t *>(packed),
                                dims, strides, box, elem, CU_TENSOR_MAP_INTERLEAVE_NONE,
@@ -677,7 +855,9 @@ int launch_tcgen05_gemm(void *out, const void *x, const float *row_scale, int64_
 
   GemmParams p{};
   p.out = out;
+  p.packed = packed;
   p.row_scale = row_scale;
+  p.table_scale = table_scale;
   p.row_norms = static_cast<const __nv_bfloat16 *>(row_norms_bf16);
   p.centroids = centroids;
   p.bias = bias;
@@ -687,10 +867,12 @@ int launch_tcgen05_gemm(void *out, const void *x, const float *row_scale, int64_
   p.k_iters = static_cast<int>(in_features / kBK);
   p.m_tiles = static_cast<int>(m_tiles);
   const int grid = static_cast<int>(m_tiles * n_tiles);
-  switch (bn) {
-    case 256: return launch_bn<256>(map_a, map_p, p, grid, stream);
-    case 192: return launch_bn<192>(map_a, map_p, p, grid, stream);
-    default: return launch_bn<128>(map_a, map_p, p, grid, stream);
+  switch (bits) {
+    case 2: return launch_bits<2>(bn, map_a, map_p, p, grid, stream);
+    case 3: return launch_bits<3>(bn, map_a, map_p, p, grid, stream);
+    case 4: return launch_bits<4>(bn, map_a, map_p, p, grid, stream);
+    case 6: return launch_bits<6>(bn, map_a, map_p, p, grid, stream);
+    default: return launch_bits<8>(bn, map_a, map_p, p, grid, stream);
   }
 }
 

@@ -18,6 +18,7 @@
 // Butterfly widths run in increasing order and every pair computes (l + r, l - r) with l
 // the lower index, which keeps the fp32 result bit-identical to the reference's kernels.
 #include "common.cuh"
+#include "table_scale.cuh"
 
 namespace oq {
 namespace {
@@ -50,6 +51,10 @@ struct PrologueParams {
   // operands in one 16-bit format.
   int f16_operand;
   float *row_scale;
+  // When set, CTA 0 also picks the scale of the GEMM's f16 weight table (table_scale.cuh).
+  const float *w_centroids;
+  int w_bits;
+  float *table_scale_out;
 };
 
 // Number of boundaries strictly below `v` (sorted ascending, count = 2^bits - 1), as a
@@ -193,6 +198,9 @@ rotate_quantize_kernel(const PrologueParams p) {
   float *s_inv = s_norm + 8;     // [R] 1/(norm+eps)
   float *s_opscale = s_inv + 8;  // [R] 2^(14 - E) in f16 operand mode
 
+  if (blockIdx.x == 0 && p.table_scale_out != nullptr) {
+    search_table_scale(p.w_centroids, p.w_bits, p.table_scale_out, s_bnd);  // tables not filled yet
+  }
   const int levels = 1 << p.bits;
   for (int i = threadIdx.x; i < levels; i += kThreads) {
     s_cent[i] = p.centroids[i];
@@ -437,7 +445,10 @@ int launch_rotate_quantize(const void *x, int x_dtype, int64_t rows, int64_t dim
                            const int32_t *perm, const int8_t *signs, int64_t block,
                            const float *boundaries, const float *centroids, int bits, float eps,
                            void *x_q, uint8_t *codes, float *norms, float *f16_row_scale,
+                           const float *w_centroids, int w_bits, float *table_scale_out,
                            cudaStream_t stream) {
+  OQ_CHECK_ARG(table_scale_out == nullptr || (w_centroids != nullptr && w_bits >= 1 && w_bits <= 8),
+               "the table scale search needs the weight codebook");
   OQ_CHECK_ARG(f16_row_scale == nullptr || (x_dtype != OQ_DTYPE_F32 && x_q != nullptr),
                "the f16 operand output needs 16-bit activations and an output buffer");
   OQ_CHECK_ARG(valid_dtype(x_dtype), "x must be float32, float16, or bfloat16");
@@ -508,6 +519,9 @@ int launch_rotate_quantize(const void *x, int x_dtype, int64_t rows, int64_t dim
   p.inv_sqrt_block = static_cast<float>(1.0 / sqrt(static_cast<double>(block)));
   p.f16_operand = f16_row_scale != nullptr ? 1 : 0;
   p.row_scale = f16_row_scale;
+  p.w_centroids = w_centroids;
+  p.w_bits = w_bits;
+  p.table_scale_out = table_scale_out;
 
   const int64_t ctas_needed = (rows + rows_per_cta - 1) / rows_per_cta;
   const int grid = static_cast<int>(std::min<int64_t>(ctas_needed, static_cast<int64_t>(sm_count) * 8));

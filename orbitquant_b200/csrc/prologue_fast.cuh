@@ -102,6 +102,9 @@ rotate_quantize_fast_kernel(const PrologueParams p) {
   float *s_opscale = s_inv + 8;                                                     // [8]
   uint16_t *s_outtab = reinterpret_cast<uint16_t *>(s_opscale + 8);                 // [R][kLevels]
 
+  if (blockIdx.x == 0 && p.table_scale_out != nullptr) {
+    search_table_scale(p.w_centroids, p.w_bits, p.table_scale_out, rot);  // token buffers still free
+  }
   for (int i = threadIdx.x; i < kLevels; i += kFastThreads) {
     s_cent[i] = p.centroids[i];
     s_bnd[i] = i < kLevels - 1 ? p.boundaries[i] : 0.0f;

@@ -39,8 +39,9 @@ _SIGNATURES = {
                                        _vp, _vp, _int, _int, _int, _vp, _sz, _vp]),
     "oq_matmul_workspace_bytes": (_sz, [_i64, _i64, _i64, _int, _int, _int, _int]),
     "oq_gemm_tcgen05_supported": (_int, [_i64, _i64, _i64, _int, _int, _int]),
-    "oq_gemm_tcgen05_f16": (_int, [_vp, _vp, _vp, _i64, _i64, _i64, _vp, _i64, _vp, _vp, _vp, _int, _vp]),
-    "oq_rows_to_f16_operand": (_int, [_vp, _int, _i64, _i64, _vp, _vp, _vp]),
+    "oq_gemm_tcgen05_f16": (_int, [_vp, _vp, _vp, _vp, _i64, _i64, _i64, _vp, _i64, _int, _vp, _vp, _vp,
+                                   _int, _vp]),
+    "oq_rows_to_f16_operand": (_int, [_vp, _int, _i64, _i64, _vp, _vp, _vp, _int, _vp, _vp]),
     "oq_linear_forward": (_int, [_vp, _vp, _int, _i64, _i64, _i64, _vp, _i64, _int, _vp, _vp,
                                  _vp, _int, _vp, _vp, _i64, _vp, _vp, _int, _f32, _int, _int,
                                  _vp, _sz, _vp]),
@@ -242,20 +243,29 @@ def matmul_packed_weight(x, packed_weight_indices, row_norms, centroids, *, bits
     return out.reshape(*x.shape[:-1], out_features)
 
 
-def rows_to_f16_operand(x):
-    """``x`` (bf16/f16 ``[rows, K]``) -> (f16 operand, per-token power-of-two factors)."""
+def rows_to_f16_operand(x, centroids=None):
+    """``x`` (bf16/f16 ``[rows, K]``) -> (f16 operand, per-token power-of-two factors, table
+    scale).  The table scale (a 1-element f32 tensor) is searched for ``centroids`` when
+    given, else ``None``."""
     _require_cuda("x", x)
     x2 = x.contiguous().reshape(-1, x.shape[-1])
     out = torch.empty(x2.shape, dtype=torch.float16, device=x.device)
     scale = torch.empty(x2.shape[0], dtype=torch.float32, device=x.device)
+    table = None
+    bits = 0
+    if centroids is not None:
+        centroids = centroids.to(device=x.device, dtype=torch.float32).contiguous()
+        bits = int(centroids.numel()).bit_length() - 1
+        table = torch.empty(1, dtype=torch.float32, device=x.device)
     with torch.cuda.device(x.device):
         _check(load().oq_rows_to_f16_operand(_ptr(x2), DTYPE_CODES[x.dtype], x2.shape[0], x2.shape[1],
-                                             _ptr(out), _ptr(scale), _stream(x.device)))
-    return out, scale
+                                             _ptr(out), _ptr(scale), _ptr(centroids), bits,
+                                             _ptr(table), _stream(x.device)))
+    return out, scale, table
 
 
-def gemm_tcgen05_f16(x_f16, row_scale, packed, row_norms, centroids, *, out_features, bias=None,
-                     out=None):
+def gemm_tcgen05_f16(x_f16, row_scale, packed, row_norms, centroids, *, out_features, bits=4,
+                     bias=None, out=None, table_scale=None):
     """The tcgen05 GEMM alone on a prepared f16 operand; all tensors already on the device
     with their final dtypes (uint8 / bf16 / f32), nothing is converted here."""
     _require_cuda("x_f16", x_f16)
@@ -265,9 +275,9 @@ def gemm_tcgen05_f16(x_f16, row_scale, packed, row_norms, centroids, *, out_feat
     bias_code = 0 if bias is None else DTYPE_CODES[bias.dtype]
     with torch.cuda.device(x_f16.device):
         _check(load().oq_gemm_tcgen05_f16(
-            _ptr(out), _ptr(x_f16), _ptr(row_scale), rows, k, out_features, _ptr(packed),
-            packed.numel(), _ptr(row_norms), _ptr(centroids), _ptr(bias), bias_code,
-            _stream(x_f16.device)))
+            _ptr(out), _ptr(x_f16), _ptr(row_scale), _ptr(table_scale), rows, k, out_features,
+            _ptr(packed), packed.numel(), int(bits), _ptr(row_norms), _ptr(centroids), _ptr(bias),
+            bias_code, _stream(x_f16.device)))
     return out
 
 

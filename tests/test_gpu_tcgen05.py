@@ -57,6 +57,53 @@ def test_tcgen05_every_tile_width(oracle, tile_n, monkeypatch):
     _check_close(y, ref, ("tile", tile_n))
 
 
+@pytest.mark.parametrize("tile_n", ["128", "192", "256"])
+@pytest.mark.parametrize("bits", [2, 3, 6, 8])
+def test_tcgen05_other_bit_widths(oracle, golden_codebooks, bits, tile_n, monkeypatch):
+    """2/3-bit tables decode through register byte-permutes, 6/8-bit through a shared-memory
+    table; 3-bit tiles are the one width the expanders fetch from global memory themselves."""
+    from conftest import codebook_from_golden
+    dev = _dev()
+    monkeypatch.setenv("ORBIT_B200_TILE_N", tile_n)
+    native.gemm_clear_device_status()
+    rows, k, n = 300, 768, 456
+    idx, packed, rn, bias = _random_layer(k, n, bits, seed=bits * 11)
+    cent = (codebook_from_golden(golden_codebooks, k, 8) if bits == 8 else get_codebook(k, bits)).centroids
+    x = (torch.randn(rows, k) * 0.9).to(torch.bfloat16)
+    y = native.matmul_packed_weight(x.to(dev), packed.to(dev), rn, cent, bits=bits, out_features=n,
+                                    in_features=k, bias=bias, kernel=native.KERNEL_TCGEN05)
+    _assert_status_clean()
+    ref, _ = oracle.matmul_packed(x, packed, rn, cent, bits=bits, out_features=n, bias=bias,
+                                  mode=oracle.MM_FP32_CENTROIDS)
+    _check_close(y, ref, ("bits", bits, "tile", tile_n))
+
+
+def test_mixed_bit_modules_use_the_tensor_core_kernel(oracle):
+    """The mixed-bit policy shapes (W2A4 for Q/K, W3A3 elsewhere) at a row count that takes
+    the tcgen05 kernel by default."""
+    dev = _dev()
+    torch.manual_seed(21)
+    for wb, ab in ((2, 4), (3, 3)):
+        cfg = OrbitQuantConfig(weight_bits=wb, activation_bits=ab, rotation_seed=2)
+        lin = torch.nn.Linear(3072, 384)
+        with torch.no_grad():
+            lin.weight.mul_(0.02 / lin.weight.std())
+        module = OrbitQuantLinear.from_linear(lin, config=cfg, module_name="mixed").to(dev)
+        x = torch.randn(260, 3072)
+        x[:, :15] *= 20
+        x = x.to(torch.bfloat16)
+        assert native.load().oq_gemm_tcgen05_supported(260, 3072, 384, wb, 2, 0) == 1
+        y = module(x.to(dev))
+        _assert_status_clean()
+        ref, _ = oracle.linear_forward(
+            x, module.packed_weight_indices.cpu(), module.row_norms.cpu(), module.bias.detach().cpu(),
+            perm=module.rotation.permutation, signs=module.rotation.signs,
+            block=module.rotation.block_size, act_boundaries=module.activation_codebook.boundaries,
+            act_centroids=module.activation_codebook.centroids,
+            w_centroids=module.weight_codebook.centroids, w_bits=wb, out_features=384)
+        _check_close(y, ref, ("mixed", wb, ab))
+
+
 def test_f16_operand_rescaling_is_exact():
     """Token scales spanning 2^-40 .. 2^40 must not change the result beyond the scale."""
     dev = _dev()
@@ -69,7 +116,7 @@ def test_f16_operand_rescaling_is_exact():
     y2 = _run((base.float() * scales).to(torch.bfloat16).to(dev), packed.to(dev), rn, cent, n, k, None,
               native.KERNEL_TCGEN05).float().cpu()
     assert torch.allclose(y2 / scales, y1, rtol=1e-2, atol=0)   # bf16 output rounding only
-    operand, factor = native.rows_to_f16_operand(base.to(dev))
+    operand, factor, _ = native.rows_to_f16_operand(base.to(dev))
     assert torch.equal((operand.float() * factor[:, None]).cpu(), base.float())
 
 

@@ -275,6 +275,8 @@ def test_argument_errors_surface_without_a_gpu():
     assert lib.oq_linear_workspace_bytes(16, 768, 2304, 4, 2, 0, 0) == 16 * 768 * 2
     assert lib.oq_gemm_tcgen05_supported(4608, 3072, 9216, 4, 2, 0) == 1
     assert lib.oq_gemm_tcgen05_supported(4608, 3070, 9216, 4, 2, 0) == 0
+    assert lib.oq_gemm_tcgen05_supported(4608, 3072, 9216, 3, 2, 0) == 1
+    assert lib.oq_gemm_tcgen05_supported(4608, 3072, 9216, 5, 2, 0) == 0
     with pytest.raises(RuntimeError, match="CUDA"):
         native.matmul_packed_weight(torch.zeros(2, 64), torch.zeros(256, dtype=torch.uint8),
                                     torch.zeros(8), torch.zeros(16), bits=4, out_features=8,
