@@ -47,9 +47,7 @@ namespace {
 
 constexpr int kBM = 256;
 constexpr int kBK = 64;
-constexpr int kThreads = 320;
-constexpr int kProducerWarp = 8;
-constexpr int kMmaWarp = 9;
+constexpr int kEpilogueWarps = 8;  // two accumulators x four TMEM lane quarters
 constexpr float kCentroidScale = kTableScaleBase;  // table scale when none was searched
 constexpr uint32_t kSpinLimit = 1u << 22;
 
@@ -74,7 +72,13 @@ struct Tile {
   static_assert(kStages >= 2, "tile does not fit in shared memory");
   static constexpr int kSmemBytes = kHeaderBytes + 1024 /*alignment slack*/ + kStages * kStageBytes;
   static constexpr int kTmemCols = BN == 128 ? 256 : 512;  // power of two >= 2 * BN
-  static constexpr int kExpanderWarps = BN == 128 ? 8 : BN / 32;  // warps that own weight rows
+  // expander threads per weight row: the decode of one k step has to finish well inside the
+  // MMA time of that step, so rows are split over 2 (or 4) threads
+  static constexpr int kTpr = BN == 128 ? (BITS == 3 ? 2 : 4) : 2;
+  static constexpr int kExpanderWarps = BN * kTpr / 32;
+  static constexpr int kProducerWarp = kExpanderWarps;
+  static constexpr int kMmaWarp = kExpanderWarps + 1;
+  static constexpr int kThreads = (kExpanderWarps + 2) * 32;
 };
 
 struct GemmParams {
@@ -90,6 +94,7 @@ struct GemmParams {
   int64_t out_features;
   int k_iters;
   int m_tiles;
+  int debug_skip;  // profiling only (ORBIT_B200_DEBUG_SKIP): 1 = expanders skip the decode
 };
 
 // ---- PTX wrappers ------------------------------------------------------------------------
@@ -327,7 +332,7 @@ __device__ __forceinline__ void group_bits(const uint32_t (&words)[NWORDS], int 
 }
 
 template <int BN, int BITS>
-__global__ void __launch_bounds__(kThreads, 1)
+__global__ void __launch_bounds__((Tile<BN, BITS>::kThreads), 1)
 gemm_w4_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
                        const __grid_constant__ CUtensorMap map_p, const GemmParams p) {
   using T = Tile<BN, BITS>;
@@ -371,29 +376,29 @@ gemm_w4_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
     *s_abort = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
-  if (warp == kMmaWarp) {
+  if (warp == T::kMmaWarp) {
     tmem_alloc(smem_u32(s_tmem), T::kTmemCols);
   }
-  if (warp == kProducerWarp && lane == 0) {
+  if (warp == T::kProducerWarp && lane == 0) {
     asm volatile("prefetch.tensormap [%0];" ::"l"(&map_a) : "memory");
     asm volatile("prefetch.tensormap [%0];" ::"l"(&map_p) : "memory");
   }
-  for (int i = threadIdx.x; i < (1 << BITS); i += kThreads) {
+  for (int i = threadIdx.x; i < (1 << BITS); i += T::kThreads) {
     s_cent[i] = p.centroids[i];
   }
   __syncthreads();
   // chosen by the kernel that ran just before this one (table_scale.cuh); 2^8 without it
   const float table_scale = p.table_scale != nullptr ? __ldg(p.table_scale) : kCentroidScale;
   if (BITS == 6) {  // [entry][32 lane copies]
-    for (int i = threadIdx.x; i < 64 * 32; i += kThreads) {
+    for (int i = threadIdx.x; i < 64 * 32; i += T::kThreads) {
       s_lut[i] = __half_as_ushort(__float2half_rn(s_cent[i >> 5] * table_scale));
     }
   } else if (BITS == 8) {  // [entry][8 copies]
-    for (int i = threadIdx.x; i < 256 * 8; i += kThreads) {
+    for (int i = threadIdx.x; i < 256 * 8; i += T::kThreads) {
       s_lut[i] = __half_as_ushort(__float2half_rn(s_cent[i >> 3] * table_scale));
     }
   }
-  for (int i = threadIdx.x; i < BN; i += kThreads) {
+  for (int i = threadIdx.x; i < BN; i += T::kThreads) {
     const int64_t n = n0 + i;
     const bool ok = n < p.out_features;
     s_scale[i] = ok ? __fdiv_rn(__bfloat162float(p.row_norms[n]), table_scale) : 0.0f;
@@ -404,7 +409,7 @@ gemm_w4_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
   tc_fence_after();
   const uint32_t tmem_base = *s_tmem;
 
-  if (warp == kProducerWarp) {
+  if (warp == T::kProducerWarp) {
     if (lane == 0) {
       int issued = 0;
       for (int it = 0; it < p.k_iters; ++it) {
@@ -431,7 +436,7 @@ gemm_w4_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
         }
       }
     }
-  } else if (warp == kMmaWarp) {
+  } else if (warp == T::kMmaWarp) {
     if (lane == 0) {
       constexpr uint32_t idesc = instr_desc(BN);
       bool ok = true;
@@ -460,11 +465,11 @@ gemm_w4_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
     }
   } else {
     // ---- expanders ----
-    constexpr int kThreadsPerRow = BN == 128 ? 2 : 1;  // BN=192 leaves warps 6 and 7 without rows
+    constexpr int kThreadsPerRow = T::kTpr;
     constexpr int kBytesPerThread = T::kRowBytes / kThreadsPerRow;
     constexpr int kWords = kBytesPerThread / 4;
     constexpr int kGroups = (kBK / 8) / kThreadsPerRow;   // 16-byte output chunks per thread
-    const int et = threadIdx.x;  // 0..255
+    const int et = threadIdx.x;  // expander thread index (every expander warp owns rows)
     const int row = et / kThreadsPerRow;
     const int part = et % kThreadsPerRow;
     // Register table (2-, 3-, 4-bit): entry i = f16(centroid[i] * 2^8).
@@ -527,18 +532,23 @@ gemm_w4_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
             words[4 * q + 2] = v.z;
             words[4 * q + 3] = v.w;
           }
-        } else {
+        } else if (kBytesPerThread % 8 == 0) {
 #pragma unroll
           for (int q = 0; q < kWords / 2; ++q) {
             const uint2 v = reinterpret_cast<const uint2 *>(src)[q];
             words[2 * q] = v.x;
             words[2 * q + 1] = v.y;
           }
+        } else {
+#pragma unroll
+          for (int q = 0; q < kWords; ++q) {
+            words[q] = reinterpret_cast<const uint32_t *>(src)[q];
+          }
         }
       }
       const uint32_t dst_row = b_addr(s) + row_off;
 #pragma unroll
-      for (int c = 0; c < kGroups; ++c) {
+      for (int c = 0; c < (p.debug_skip ? 0 : kGroups); ++c) {
         uint32_t lo;
         uint32_t hi;
         group_bits<BITS, kWords>(words, c, lo, hi);
@@ -574,7 +584,7 @@ gemm_w4_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
     }
 
     // ---- epilogue: warp w reads accumulator w/4, TMEM lanes 32*(w%4).. ----
-    if (ok && mbar_wait(acc_full_bar, 0, s_abort, 5)) {
+    if (ok && warp < kEpilogueWarps && mbar_wait(acc_full_bar, 0, s_abort, 5)) {
       tc_fence_after();
       const int half = warp >> 2;
       const int quarter = warp & 3;
@@ -621,7 +631,7 @@ gemm_w4_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
 
   tc_fence_before();
   __syncthreads();
-  if (warp == kMmaWarp) {
+  if (warp == T::kMmaWarp) {
     tc_fence_after();
     tmem_dealloc(tmem_base, T::kTmemCols);
   }
@@ -727,7 +737,7 @@ int launch_bn(const CUtensorMap &map_a, const CUtensorMap &map_p, const GemmPara
                                        Tile<BN, BITS>::kSmemBytes);
   });
   OQ_CHECK_CUDA(attr_status);
-  gemm_w4_tcgen05_kernel<BN, BITS><<<grid, kThreads, Tile<BN, BITS>::kSmemBytes, stream>>>(map_a, map_p, p);
+  gemm_w4_tcgen05_kernel<BN, BITS><<<grid, Tile<BN, BITS>::kThreads, Tile<BN, BITS>::kSmemBytes, stream>>>(map_a, map_p, p);
   OQ_CHECK_CUDA(cudaGetLastError());
   count_launch();
   return OQ_OK;
@@ -866,6 +876,9 @@ int launch_tcgen05_gemm(void *out, const void *x, const float *row_scale, const 
   p.out_features = out_features;
   p.k_iters = static_cast<int>(in_features / kBK);
   p.m_tiles = static_cast<int>(m_tiles);
+  if (const char *skip = getenv("ORBIT_B200_DEBUG_SKIP")) {
+    p.debug_skip = atoi(skip);
+  }
   const int grid = static_cast<int>(m_tiles * n_tiles);
   switch (bits) {
     case 2: return launch_bits<2>(bn, map_a, map_p, p, grid, stream);

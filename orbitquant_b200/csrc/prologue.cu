@@ -17,6 +17,8 @@
 //
 // Butterfly widths run in increasing order and every pair computes (l + r, l - r) with l
 // the lower index, which keeps the fp32 result bit-identical to the reference's kernels.
+#include <cstdlib>
+
 #include "common.cuh"
 #include "table_scale.cuh"
 
@@ -493,6 +495,12 @@ int launch_rotate_quantize(const void *x, int x_dtype, int64_t rows, int64_t dim
     rows_per_cta = r;
     if ((r * chunks) % kWarps == 0) {
       break;
+    }
+  }
+  if (const char *forced = getenv("ORBIT_B200_PROLOGUE_ROWS")) {  // profiling only
+    const int value = atoi(forced);
+    if (value >= 1 && value <= 8 && value <= rows) {
+      rows_per_cta = value;
     }
   }
   const size_t smem = fast != nullptr ? fast_smem_bytes(static_cast<int>(dim), rows_per_cta, bits)

@@ -42,7 +42,11 @@ __device__ __forceinline__ void radix_butterflies(float (&v)[S]) {
   }
 }
 
-template <int BITS, int S, bool LAST>
+// One pass over butterfly widths stride .. stride*S/2.  U column groups are processed
+// together so that U*S independent boundary searches are in flight per thread: the search
+// is a chain of dependent shared-memory reads, and without that much instruction-level
+// parallelism its latency, not any throughput limit, sets the pace of the whole kernel.
+template <int BITS, int S, int U, bool LAST>
 __device__ __forceinline__ void fast_strided_pass(float *rot, uint16_t *stage, const unsigned char *bnd,
                                                   const uint16_t *outtab, int dim, int nrows,
                                                   int stride, float inv_sqrt_block) {
@@ -53,24 +57,62 @@ __device__ __forceinline__ void fast_strided_pass(float *rot, uint16_t *stage, c
     float *row = rot + r * dim;
     uint16_t *stage_row = stage + r * dim;
     const unsigned char *tab = reinterpret_cast<const unsigned char *>(outtab + (r << BITS));
-    for (int c = 0; c < cols; ++c) {
-      const int base = (c >> sq_log2) * (stride * S) + (c & sq_mask) * 256 + static_cast<int>(threadIdx.x);
-      float v[S];
+    for (int c0 = 0; c0 < cols; c0 += U) {
+      int base[U];
+      float v[U][S];
 #pragma unroll
-      for (int s = 0; s < S; ++s) {
-        v[s] = row[base + s * stride];
+      for (int u = 0; u < U; ++u) {
+        const int c = c0 + u;
+        base[u] = (c >> sq_log2) * (stride * S) + (c & sq_mask) * 256 + static_cast<int>(threadIdx.x);
+#pragma unroll
+        for (int s = 0; s < S; ++s) {
+          v[u][s] = row[base[u] + s * stride];
+        }
       }
-      radix_butterflies<S>(v);
 #pragma unroll
-      for (int s = 0; s < S; ++s) {
-        if (LAST) {
-          const uint32_t off = search_offset<BITS>(__fmul_rn(v[s], inv_sqrt_block), bnd);
-          stage_row[base + s * stride] = *reinterpret_cast<const uint16_t *>(tab + (off >> 1));
-        } else {
-          row[base + s * stride] = v[s];
+      for (int u = 0; u < U; ++u) {
+        radix_butterflies<S>(v[u]);
+      }
+      if (LAST) {
+        uint32_t off[U][S];
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+#pragma unroll
+          for (int s = 0; s < S; ++s) {
+            off[u][s] = search_offset<BITS>(__fmul_rn(v[u][s], inv_sqrt_block), bnd);
+          }
+        }
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+#pragma unroll
+          for (int s = 0; s < S; ++s) {
+            stage_row[base[u] + s * stride] = *reinterpret_cast<const uint16_t *>(tab + (off[u][s] >> 1));
+          }
+        }
+      } else {
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+#pragma unroll
+          for (int s = 0; s < S; ++s) {
+            row[base[u] + s * stride] = v[u][s];
+          }
         }
       }
     }
+  }
+}
+
+template <int BITS, int S, bool LAST>
+__device__ __forceinline__ void fast_strided_unroll(float *rot, uint16_t *stage, const unsigned char *bnd,
+                                                    const uint16_t *outtab, int dim, int nrows, int stride,
+                                                    float isb) {
+  const int cols = dim / (S * 256);
+  if (S <= 4 && cols % 3 == 0) {
+    fast_strided_pass<BITS, S, 3, LAST>(rot, stage, bnd, outtab, dim, nrows, stride, isb);
+  } else if (S <= 8 && cols % 2 == 0) {
+    fast_strided_pass<BITS, S, 2, LAST>(rot, stage, bnd, outtab, dim, nrows, stride, isb);
+  } else {
+    fast_strided_pass<BITS, S, 1, LAST>(rot, stage, bnd, outtab, dim, nrows, stride, isb);
   }
 }
 
@@ -79,10 +121,10 @@ __device__ __forceinline__ void fast_strided_any(float *rot, uint16_t *stage, co
                                                  const uint16_t *outtab, int dim, int nrows, int stride,
                                                  int radix, float isb) {
   switch (radix) {
-    case 2: fast_strided_pass<BITS, 2, LAST>(rot, stage, bnd, outtab, dim, nrows, stride, isb); break;
-    case 4: fast_strided_pass<BITS, 4, LAST>(rot, stage, bnd, outtab, dim, nrows, stride, isb); break;
-    case 8: fast_strided_pass<BITS, 8, LAST>(rot, stage, bnd, outtab, dim, nrows, stride, isb); break;
-    default: fast_strided_pass<BITS, 16, LAST>(rot, stage, bnd, outtab, dim, nrows, stride, isb); break;
+    case 2: fast_strided_unroll<BITS, 2, LAST>(rot, stage, bnd, outtab, dim, nrows, stride, isb); break;
+    case 4: fast_strided_unroll<BITS, 4, LAST>(rot, stage, bnd, outtab, dim, nrows, stride, isb); break;
+    case 8: fast_strided_unroll<BITS, 8, LAST>(rot, stage, bnd, outtab, dim, nrows, stride, isb); break;
+    default: fast_strided_unroll<BITS, 16, LAST>(rot, stage, bnd, outtab, dim, nrows, stride, isb); break;
   }
 }
 
