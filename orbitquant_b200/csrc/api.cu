@@ -1,4 +1,5 @@
 // extern "C" surface of liborbit_b200.so: argument validation, kernel choice, status.
+#include <cstdlib>
 #include <cstring>
 
 #include "common.cuh"
@@ -32,6 +33,13 @@ int launch_small_rows(void *out, const void *x, int dtype, int64_t rows, int64_t
                       int bias_dtype, int weight_mode, cudaStream_t stream);
 bool small_rows_supported(int64_t rows, int64_t in_features, int64_t out_features, int bits,
                           int dtype, int weight_mode);
+bool stream_rows_preferred(int64_t rows, int64_t in_features, int64_t out_features, int bits,
+                           int dtype);
+size_t stream_rows_workspace_bytes(int64_t in_features, int64_t out_features);
+int launch_stream_rows(void *out, const void *x, int64_t rows, int64_t in_features,
+                       int64_t out_features, const uint8_t *packed, const void *row_norms_bf16,
+                       const float *centroids, const void *bias, int bias_dtype, int weight_mode,
+                       void *workspace, size_t workspace_bytes, cudaStream_t stream);
 int launch_unpack(const uint8_t *packed, int bits, int64_t count, uint8_t *values,
                   cudaStream_t stream);
 int launch_pack(const uint8_t *values, int bits, int64_t count, uint8_t *packed,
@@ -91,6 +99,23 @@ int choose_kernel(int kernel, int64_t rows, int64_t in_features, int64_t out_fea
     return OQ_KERNEL_TCGEN05;
   }
   return OQ_KERNEL_TILED;
+}
+
+// Within the small-rows family: large layers go to the persistent streaming kernel.
+// ORBIT_B200_STREAM_ROWS=0 / 1 forces one or the other (for A/B timing).
+bool use_stream_rows(int64_t rows, int64_t in_features, int64_t out_features, int bits, int dtype) {
+  static const int forced = [] {
+    const char *env = std::getenv("ORBIT_B200_STREAM_ROWS");
+    return env == nullptr ? -1 : std::atoi(env);
+  }();
+  if (forced == 0) {
+    return false;
+  }
+  const bool fits = stream_rows_preferred(rows, in_features, out_features, bits, dtype);
+  if (forced > 0) {
+    return rows >= 1 && rows <= 16 && bits == 4 && dtype == OQ_DTYPE_BF16 && in_features % 128 == 0;
+  }
+  return fits;
 }
 
 // Bytes of the f16 operand [rows, K] (256-aligned); the per-token factors follow it.
@@ -180,7 +205,11 @@ size_t oq_matmul_workspace_bytes(int64_t rows, int64_t in_features, int64_t out_
     return 0;
   }
   const int mode = resolve_weight_mode(weight_mode);
-  if (choose_kernel(kernel, rows, in_features, out_features, bits, dtype, mode) != OQ_KERNEL_TCGEN05) {
+  const int chosen = choose_kernel(kernel, rows, in_features, out_features, bits, dtype, mode);
+  if (chosen == OQ_KERNEL_SMALL_ROWS && use_stream_rows(rows, in_features, out_features, bits, dtype)) {
+    return stream_rows_workspace_bytes(in_features, out_features);
+  }
+  if (chosen != OQ_KERNEL_TCGEN05) {
     return 0;
   }
   return f16_operand_bytes(rows, in_features) + align_up(static_cast<size_t>(rows + 1) * 4, 256);
@@ -214,6 +243,10 @@ int oq_matmul_packed_weight(void *out, const void *x, int dtype, int64_t rows, i
     case OQ_KERNEL_SMALL_ROWS:
       if (!small_rows_supported(rows, in_features, out_features, bits, dtype, mode)) {
         return fail(OQ_ERR_UNSUPPORTED, "the small-rows kernel does not take this problem");
+      }
+      if (use_stream_rows(rows, in_features, out_features, bits, dtype)) {
+        return launch_stream_rows(out, x, rows, in_features, out_features, packed, row_norms_bf16,
+                                  centroids, bias, bias_dtype, mode, workspace, workspace_bytes, s);
       }
       return launch_small_rows(out, x, dtype, rows, in_features, out_features, packed, bits,
                                row_norms_bf16, centroids, bias, bias_dtype, mode, s);
@@ -298,7 +331,10 @@ size_t oq_linear_workspace_bytes(int64_t rows, int64_t in_features, int64_t out_
     // the prologue writes the f16 operand and its per-token factors straight into it
     return f16_operand_bytes(rows, in_features) + align_up(static_cast<size_t>(rows + 1) * 4, 256);
   }
-  return align_up(static_cast<size_t>(rows) * in_features * dtype_size(dtype), 256);
+  // quantised activations, then whatever the matmul kernel wants for itself
+  return align_up(static_cast<size_t>(rows) * in_features * dtype_size(dtype), 256) +
+         oq_matmul_workspace_bytes(rows, in_features, out_features, weight_bits, dtype, weight_mode,
+                                   kernel == OQ_KERNEL_AUTO ? OQ_KERNEL_AUTO : kernel);
 }
 
 int oq_linear_forward(void *out, const void *x, int dtype, int64_t rows, int64_t in_features,
@@ -354,9 +390,12 @@ int oq_linear_forward(void *out, const void *x, int dtype, int64_t rows, int64_t
                                       nullptr, nullptr, 0, nullptr, s)) {
     return rc;
   }
+  const size_t xq_bytes = align_up(static_cast<size_t>(rows) * in_features * dtype_size(dtype), 256);
   return oq_matmul_packed_weight(out, workspace, dtype, rows, in_features, out_features, packed,
                                  packed_bytes, weight_bits, row_norms_bf16, weight_centroids, bias,
-                                 bias_dtype, weight_mode, chosen, nullptr, 0, stream);
+                                 bias_dtype, weight_mode, chosen,
+                                 static_cast<unsigned char *>(workspace) + xq_bytes,
+                                 workspace_bytes - xq_bytes, stream);
 }
 
 // Status word of the tcgen05 kernel's bounded waits (0 = every wait completed).  Reading

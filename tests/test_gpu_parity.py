@@ -225,6 +225,29 @@ def test_small_rows_and_tiled_agree_and_are_deterministic():
     _check_close(a, c, "small_rows vs tiled")
 
 
+@pytest.mark.parametrize("mode", ["centroid", "bf16_scaled"])
+@pytest.mark.parametrize("rows,k,n,with_bias", [
+    (1, 3072, 3072, True),      # one k range, epilogue inside the kernel
+    (16, 3072, 9216, True),
+    (5, 12288, 1030, False),    # several k ranges, ragged last 8-row block
+    (9, 4736, 1536, True),      # 37 k steps: the last range is shorter than the others
+    (16, 13824, 1024, True),
+])
+def test_streaming_small_rows_kernel_vs_oracle(oracle, mode, rows, k, n, with_bias):
+    """Layers of a few megabytes and more take the persistent weight-streaming kernel
+    (same C entry point, chosen by size)."""
+    dev = _dev()
+    idx, packed, rn, bias = _random_layer(k, n, 4, seed=rows + n, bias=with_bias)
+    cent = get_codebook(k, 4).centroids
+    x = (torch.randn(rows, k) * 1.5).to(torch.bfloat16)
+    args = dict(bits=4, out_features=n, in_features=k, bias=bias,
+                weight_mode=native.WEIGHT_MODE_NAMES[mode], kernel=native.KERNEL_SMALL_ROWS)
+    y = native.matmul_packed_weight(x.to(dev), packed.to(dev), rn, cent, **args)
+    _check_close(y, _oracle_matmul(oracle, x, packed, rn, cent, 4, n, bias, mode), (mode, rows, k, n))
+    again = native.matmul_packed_weight(x.to(dev), packed.to(dev), rn, cent, **args)
+    assert torch.equal(y, again), "not deterministic"
+
+
 def test_matmul_argument_errors():
     dev = _dev()
     x = torch.zeros(4, 64, dtype=torch.bfloat16, device=dev)
