@@ -55,6 +55,7 @@ def build(force: bool = False, verbose: bool = False, ptxas_info: bool = False) 
     flags = list(NVCC_FLAGS)
     if ptxas_info:
         flags += ["-Xptxas", "-v"]
+    flags += os.environ.get("ORBIT_B200_NVCC_EXTRA", "").split()  # e.g. -DORBIT_TRACE
     # A host compiler that links libstdc++ statically breaks std::call_once in a shared
     # object; prefer the system one.
     if Path("/usr/bin/g++").exists():

@@ -22,7 +22,7 @@ int launch_rotate_quantize(const void *x, int x_dtype, int64_t rows, int64_t dim
                            const float *boundaries, const float *centroids, int bits, float eps,
                            void *x_q, uint8_t *codes, float *norms, float *f16_row_scale,
                            const float *w_centroids, int w_bits, float *table_scale_out,
-                           cudaStream_t stream);
+                           int *zero_words, int zero_count, cudaStream_t stream);
 int launch_tiled_matmul(void *out, const void *x, int dtype, int64_t rows, int64_t in_features,
                         int64_t out_features, const uint8_t *packed, int bits,
                         const void *row_norms_bf16, const float *centroids, const void *bias,
@@ -51,11 +51,21 @@ bool tcgen05_gemm_supported(int64_t rows, int64_t in_features, int64_t out_featu
                             int dtype, int weight_mode);
 int launch_rows_to_f16(const void *x, int dtype, int64_t rows, int64_t dim, void *out_f16,
                        float *row_scale, const float *centroids, int bits, float *table_scale_out,
-                       cudaStream_t stream);
+                       int *zero_words, int zero_count, cudaStream_t stream);
 int launch_tcgen05_gemm(void *out, const void *x_f16, const float *row_scale,
                         const float *table_scale, int64_t rows, int64_t in_features, int64_t out_features, const uint8_t *packed, int bits,
                         const void *row_norms_bf16, const float *centroids, const void *bias,
                         int bias_dtype, cudaStream_t stream);
+bool tcgen05_skinny_supported(int64_t rows, int64_t in_features, int64_t out_features, int bits,
+                              int dtype, int weight_mode);
+size_t tcgen05_skinny_workspace_bytes(int64_t rows, int64_t in_features, int64_t out_features);
+int tcgen05_skinny_counter_words(int64_t rows, int64_t in_features, int64_t out_features);
+int launch_tcgen05_skinny(void *out, const void *x_f16, const float *row_scale,
+                          const float *table_scale, int64_t rows, int64_t in_features,
+                          int64_t out_features, const uint8_t *packed, int bits,
+                          const void *row_norms_bf16, const float *centroids, const void *bias,
+                          int bias_dtype, void *workspace, size_t workspace_bytes,
+                          cudaStream_t stream);
 int read_gemm_status(int *status);
 int clear_gemm_status();
 
@@ -86,6 +96,14 @@ int resolve_weight_mode(int weight_mode) {
 
 size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
 
+// Within the tcgen05 family: up to 128 rows go to the operand-swapped few-token kernel.
+// ORBIT_B200_SKINNY=0 keeps them on the large-row kernel (for A/B timing).
+bool use_skinny(int64_t rows, int64_t in_features, int64_t out_features, int bits, int dtype, int mode) {
+  const char *env = std::getenv("ORBIT_B200_SKINNY");
+  const bool enabled = env == nullptr || std::atoi(env) != 0;
+  return enabled && tcgen05_skinny_supported(rows, in_features, out_features, bits, dtype, mode);
+}
+
 // Kernel for a problem: the caller's explicit choice, or by shape.
 int choose_kernel(int kernel, int64_t rows, int64_t in_features, int64_t out_features, int bits,
                   int dtype, int mode) {
@@ -93,6 +111,11 @@ int choose_kernel(int kernel, int64_t rows, int64_t in_features, int64_t out_fea
     return kernel;
   }
   if (rows <= 16 && small_rows_supported(rows, in_features, out_features, bits, dtype, mode)) {
+    // layers of a few megabytes and more stream through the tensor-core few-token kernel
+    if (use_skinny(rows, in_features, out_features, bits, dtype, mode) &&
+        out_features * in_features * bits / 8 >= (int64_t(3) << 20)) {
+      return OQ_KERNEL_TCGEN05;
+    }
     return OQ_KERNEL_SMALL_ROWS;
   }
   if (rows > 16 && tcgen05_gemm_supported(rows, in_features, out_features, bits, dtype, mode)) {
@@ -121,6 +144,55 @@ bool use_stream_rows(int64_t rows, int64_t in_features, int64_t out_features, in
 // Bytes of the f16 operand [rows, K] (256-aligned); the per-token factors follow it.
 size_t f16_operand_bytes(int64_t rows, int64_t in_features) {
   return align_up(static_cast<size_t>(rows) * in_features * 2, 256);
+}
+
+// Workspace of the tcgen05 family: f16 operand | per-token factors + table scale | partial
+// sums of the few-token kernel's reduction slices.
+size_t tcgen05_head_bytes(int64_t rows, int64_t in_features) {
+  return f16_operand_bytes(rows, in_features) + align_up(static_cast<size_t>(rows + 1) * 4, 256);
+}
+
+size_t tcgen05_workspace_bytes(int64_t rows, int64_t in_features, int64_t out_features, int bits,
+                               int dtype, int mode) {
+  size_t bytes = tcgen05_head_bytes(rows, in_features);
+  if (use_skinny(rows, in_features, out_features, bits, dtype, mode)) {
+    bytes += tcgen05_skinny_workspace_bytes(rows, in_features, out_features);
+  }
+  return bytes;
+}
+
+// The few-token kernel's slice counters (head of its part of the workspace) have to be
+// cleared by the kernel that prepares the operand; NULL / 0 when there are none.
+int *tcgen05_counters(void *workspace, int64_t rows, int64_t in_features, int64_t out_features,
+                      int bits, int dtype, int mode, int *count) {
+  *count = 0;
+  if (!use_skinny(rows, in_features, out_features, bits, dtype, mode) ||
+      tcgen05_skinny_workspace_bytes(rows, in_features, out_features) == 0) {
+    return nullptr;
+  }
+  *count = tcgen05_skinny_counter_words(rows, in_features, out_features);
+  return reinterpret_cast<int *>(static_cast<unsigned char *>(workspace) +
+                                 tcgen05_head_bytes(rows, in_features));
+}
+
+// GEMM on the prepared operand at the head of `workspace`.
+int tcgen05_matmul(void *out, void *workspace, size_t workspace_bytes, int64_t rows,
+                   int64_t in_features, int64_t out_features, const uint8_t *packed, int bits,
+                   int dtype, int mode, const void *row_norms_bf16, const float *centroids,
+                   const void *bias, int bias_dtype, cudaStream_t s) {
+  float *row_scale = reinterpret_cast<float *>(static_cast<unsigned char *>(workspace) +
+                                               f16_operand_bytes(rows, in_features));
+  float *table_scale = row_scale + rows;  // one float after the per-token factors
+  if (use_skinny(rows, in_features, out_features, bits, dtype, mode)) {
+    const size_t head = tcgen05_head_bytes(rows, in_features);
+    return launch_tcgen05_skinny(out, workspace, row_scale, table_scale, rows, in_features,
+                                 out_features, packed, bits, row_norms_bf16, centroids, bias,
+                                 bias_dtype, static_cast<unsigned char *>(workspace) + head,
+                                 workspace_bytes - head, s);
+  }
+  return launch_tcgen05_gemm(out, workspace, row_scale, table_scale, rows, in_features,
+                             out_features, packed, bits, row_norms_bf16, centroids, bias,
+                             bias_dtype, s);
 }
 
 }  // namespace
@@ -187,7 +259,7 @@ int oq_quantize_activations(const void *x, int x_dtype, int64_t rows, int64_t di
     return rc;
   }
   return launch_rotate_quantize(x, x_dtype, rows, dim, perm, signs, block, boundaries, centroids,
-                                bits, eps, x_q, codes, norms, nullptr, nullptr, 0, nullptr,
+                                bits, eps, x_q, codes, norms, nullptr, nullptr, 0, nullptr, nullptr, 0,
                                 static_cast<cudaStream_t>(stream));
 }
 
@@ -212,7 +284,7 @@ size_t oq_matmul_workspace_bytes(int64_t rows, int64_t in_features, int64_t out_
   if (chosen != OQ_KERNEL_TCGEN05) {
     return 0;
   }
-  return f16_operand_bytes(rows, in_features) + align_up(static_cast<size_t>(rows + 1) * 4, 256);
+  return tcgen05_workspace_bytes(rows, in_features, out_features, bits, dtype, mode);
 }
 
 int oq_matmul_packed_weight(void *out, const void *x, int dtype, int64_t rows, int64_t in_features,
@@ -266,13 +338,15 @@ int oq_matmul_packed_weight(void *out, const void *x, int dtype, int64_t rows, i
         float *row_scale = reinterpret_cast<float *>(static_cast<unsigned char *>(workspace) +
                                                      f16_operand_bytes(rows, in_features));
         float *table_scale = row_scale + rows;  // one float after the per-token factors
+        int zero_count = 0;
+        int *zero_words = tcgen05_counters(workspace, rows, in_features, out_features, bits, dtype,
+                                           mode, &zero_count);
         if (int rc = launch_rows_to_f16(x, dtype, rows, in_features, workspace, row_scale, centroids,
-                                        bits, table_scale, s)) {
+                                        bits, table_scale, zero_words, zero_count, s)) {
           return rc;
         }
-        return launch_tcgen05_gemm(out, workspace, row_scale, table_scale, rows, in_features,
-                                   out_features, packed, bits, row_norms_bf16, centroids, bias,
-                                   bias_dtype, s);
+        return tcgen05_matmul(out, workspace, workspace_bytes, rows, in_features, out_features,
+                              packed, bits, dtype, mode, row_norms_bf16, centroids, bias, bias_dtype, s);
       }
     default:
       return launch_tiled_matmul(out, x, dtype, rows, in_features, out_features, packed, bits,
@@ -317,7 +391,7 @@ int oq_rows_to_f16_operand(const void *x, int dtype, int64_t rows, int64_t dim, 
     return rc;
   }
   return launch_rows_to_f16(x, dtype, rows, dim, x_f16, row_scale, centroids, bits, table_scale,
-                            static_cast<cudaStream_t>(stream));
+                            nullptr, 0, static_cast<cudaStream_t>(stream));
 }
 
 size_t oq_linear_workspace_bytes(int64_t rows, int64_t in_features, int64_t out_features,
@@ -329,7 +403,7 @@ size_t oq_linear_workspace_bytes(int64_t rows, int64_t in_features, int64_t out_
   if (choose_kernel(kernel, rows, in_features, out_features, weight_bits, dtype, mode) ==
       OQ_KERNEL_TCGEN05) {
     // the prologue writes the f16 operand and its per-token factors straight into it
-    return f16_operand_bytes(rows, in_features) + align_up(static_cast<size_t>(rows + 1) * 4, 256);
+    return tcgen05_workspace_bytes(rows, in_features, out_features, weight_bits, dtype, mode);
   }
   // quantised activations, then whatever the matmul kernel wants for itself
   return align_up(static_cast<size_t>(rows) * in_features * dtype_size(dtype), 256) +
@@ -375,19 +449,22 @@ int oq_linear_forward(void *out, const void *x, int dtype, int64_t rows, int64_t
     float *row_scale = reinterpret_cast<float *>(static_cast<unsigned char *>(workspace) +
                                                  f16_operand_bytes(rows, in_features));
     float *table_scale = row_scale + rows;  // one float after the per-token factors
+    int zero_count = 0;
+    int *zero_words = tcgen05_counters(workspace, rows, in_features, out_features, weight_bits,
+                                       dtype, mode, &zero_count);
     if (int rc = launch_rotate_quantize(x, dtype, rows, in_features, perm, signs, block,
                                         act_boundaries, act_centroids, act_bits, eps, workspace,
                                         nullptr, nullptr, row_scale, weight_centroids, weight_bits,
-                                        table_scale, s)) {
+                                        table_scale, zero_words, zero_count, s)) {
       return rc;
     }
-    return launch_tcgen05_gemm(out, workspace, row_scale, table_scale, rows, in_features,
-                               out_features, packed, weight_bits, row_norms_bf16, weight_centroids,
-                               bias, bias_dtype, s);
+    return tcgen05_matmul(out, workspace, workspace_bytes, rows, in_features, out_features, packed,
+                          weight_bits, dtype, mode, row_norms_bf16, weight_centroids, bias,
+                          bias_dtype, s);
   }
   if (int rc = launch_rotate_quantize(x, dtype, rows, in_features, perm, signs, block, act_boundaries,
                                       act_centroids, act_bits, eps, workspace, nullptr, nullptr,
-                                      nullptr, nullptr, 0, nullptr, s)) {
+                                      nullptr, nullptr, 0, nullptr, nullptr, 0, s)) {
     return rc;
   }
   const size_t xq_bytes = align_up(static_cast<size_t>(rows) * in_features * dtype_size(dtype), 256);

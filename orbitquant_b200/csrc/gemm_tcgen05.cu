@@ -33,6 +33,7 @@
 // drained (bounded again), tensor memory is released and the kernel returns.
 #include <cuda.h>
 
+#include <algorithm>
 #include <cstdlib>
 #include <mutex>
 
@@ -128,10 +129,26 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
   return done != 0;
 }
 
+// Non-blocking test (try_wait may suspend the thread for a while even when it then succeeds).
+__device__ __forceinline__ bool mbar_test_wait(uint32_t bar, uint32_t parity) {
+  uint32_t done;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(done)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return done != 0;
+}
+
 // Bounded wait.  Returns false (after raising the abort flag) when the barrier did not
 // flip within the spin limit or another role has already aborted.
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int *abort_flag,
                                           int code) {
+  if (mbar_test_wait(bar, parity)) {
+    return true;
+  }
   for (uint32_t spin = 0; spin < kSpinLimit; ++spin) {
     if (mbar_try_wait(bar, parity)) {
       return true;
@@ -547,27 +564,33 @@ gemm_w4_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
         }
       }
       const uint32_t dst_row = b_addr(s) + row_off;
+      // Decode every group first and store afterwards: the stores are volatile asm, which the
+      // compiler keeps in program order, and a decode-store-decode-store sequence would chain
+      // the (latency-bound) byte-permute sequences one after the other instead of overlapping them.
+      uint4 expanded[kGroups];
 #pragma unroll
-      for (int c = 0; c < (p.debug_skip ? 0 : kGroups); ++c) {
+      for (int c = 0; c < kGroups; ++c) {
         uint32_t lo;
         uint32_t hi;
         group_bits<BITS, kWords>(words, c, lo, hi);
-        uint4 o;
         if (BITS == 4) {
-          decode8_w4(lo, table, o);
+          decode8_w4(lo, table, expanded[c]);
         } else if (BITS == 3) {
-          decode8_w3(lo, table, o);
+          decode8_w3(lo, table, expanded[c]);
         } else if (BITS == 2) {
-          decode8_w2(lo, table, o);
+          decode8_w2(lo, table, expanded[c]);
         } else if (BITS == 6) {
-          decode8_lut<6, 32>(lo, hi, lane_lut, o);
+          decode8_lut<6, 32>(lo, hi, lane_lut, expanded[c]);
         } else {
-          decode8_lut<8, 8>(lo, hi, lane_lut, o);
+          decode8_lut<8, 8>(lo, hi, lane_lut, expanded[c]);
         }
+      }
+#pragma unroll
+      for (int c = 0; c < (p.debug_skip ? 0 : kGroups); ++c) {
         const int chunk = part * kGroups + c;
         const uint32_t dst = dst_row + (((chunk ^ (row & 7)) & 7) << 4);
-        asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(dst), "r"(o.x), "r"(o.y),
-                     "r"(o.z), "r"(o.w)
+        asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(dst), "r"(expanded[c].x),
+                     "r"(expanded[c].y), "r"(expanded[c].z), "r"(expanded[c].w)
                      : "memory");
       }
       if (!T::kPackedByTma) {
@@ -644,9 +667,12 @@ template <int DTYPE>
 __global__ void __launch_bounds__(256) rows_to_f16_kernel(const void *x, int64_t rows, int64_t dim,
                                                           __half *out, float *row_scale,
                                                           const float *centroids, int bits,
-                                                          float *table_scale_out) {
+                                                          float *table_scale_out, int *zero_words,
+                                                          int zero_count) {
   __shared__ float s_search[272];
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   if (blockIdx.x == 0 && table_scale_out != nullptr) {
+    clear_words(zero_words, zero_count);
     search_table_scale(centroids, bits, table_scale_out, s_search);
   }
   const int lane = threadIdx.x & 31;
@@ -743,6 +769,8 @@ int launch_bn(const CUtensorMap &map_a, const CUtensorMap &map_p, const GemmPara
   return OQ_OK;
 }
 
+#include "skinny_tcgen05.cuh"
+
 }  // namespace
 
 bool tcgen05_gemm_supported(int64_t rows, int64_t in_features, int64_t out_features, int bits,
@@ -755,16 +783,17 @@ bool tcgen05_gemm_supported(int64_t rows, int64_t in_features, int64_t out_featu
 
 int launch_rows_to_f16(const void *x, int dtype, int64_t rows, int64_t dim, void *out_f16,
                        float *row_scale, const float *centroids, int bits, float *table_scale_out,
-                       cudaStream_t stream) {
+                       int *zero_words, int zero_count, cudaStream_t stream) {
+  zero_count = zero_words != nullptr ? zero_count : 0;
   OQ_CHECK_ARG(table_scale_out == nullptr || (centroids != nullptr && bits >= 1 && bits <= 8),
                "the table scale search needs the weight codebook");
   OQ_CHECK_ARG(dtype == OQ_DTYPE_BF16 || dtype == OQ_DTYPE_F16, "16-bit activations expected");
   OQ_CHECK_ARG(dim % 8 == 0 && aligned16(x) && aligned16(out_f16), "rows must be 16-byte aligned");
   const unsigned grid = static_cast<unsigned>((rows + 7) / 8);
   if (dtype == OQ_DTYPE_BF16) {
-    rows_to_f16_kernel<OQ_DTYPE_BF16><<<grid, 256, 0, stream>>>(x, rows, dim, static_cast<__half *>(out_f16), row_scale, centroids, bits, table_scale_out);
+    rows_to_f16_kernel<OQ_DTYPE_BF16><<<grid, 256, 0, stream>>>(x, rows, dim, static_cast<__half *>(out_f16), row_scale, centroids, bits, table_scale_out, zero_words, zero_count);
   } else {
-    rows_to_f16_kernel<OQ_DTYPE_F16><<<grid, 256, 0, stream>>>(x, rows, dim, static_cast<__half *>(out_f16), row_scale, centroids, bits, table_scale_out);
+    rows_to_f16_kernel<OQ_DTYPE_F16><<<grid, 256, 0, stream>>>(x, rows, dim, static_cast<__half *>(out_f16), row_scale, centroids, bits, table_scale_out, zero_words, zero_count);
   }
   OQ_CHECK_CUDA(cudaGetLastError());
   count_launch();
@@ -887,6 +916,117 @@ int launch_tcgen05_gemm(void *out, const void *x, const float *row_scale, const 
     case 6: return launch_bits<6>(bn, map_a, map_p, p, grid, stream);
     default: return launch_bits<8>(bn, map_a, map_p, p, grid, stream);
   }
+}
+
+// Few tokens (rows <= 128): the operand-swapped kernel of skinny_tcgen05.cuh.
+bool tcgen05_skinny_supported(int64_t rows, int64_t in_features, int64_t out_features, int bits,
+                              int dtype, int weight_mode) {
+  return rows <= kSkMaxTokens &&
+         tcgen05_gemm_supported(rows, in_features, out_features, bits, dtype, weight_mode);
+}
+
+size_t tcgen05_skinny_workspace_bytes(int64_t rows, int64_t in_features, int64_t out_features) {
+  // sized for the larger of two machine widths so that the figure does not depend on the
+  // device that happens to be current when the caller asks
+  const size_t a = skinny_partial_bytes(skinny_plan(rows, in_features, out_features, 148), out_features);
+  const size_t b = skinny_partial_bytes(skinny_plan(rows, in_features, out_features, 256), out_features);
+  return a > b ? a : b;
+}
+
+// Ints at the head of the few-token kernel's workspace that the preceding kernel must clear.
+int tcgen05_skinny_counter_words(int64_t rows, int64_t in_features, int64_t out_features) {
+  (void)rows;
+  (void)in_features;
+  return static_cast<int>((out_features + kSkRows - 1) / kSkRows) * 4;
+}
+
+int launch_tcgen05_skinny(void *out, const void *x, const float *row_scale, const float *table_scale,
+                          int64_t rows, int64_t in_features, int64_t out_features,
+                          const uint8_t *packed, int bits, const void *row_norms_bf16,
+                          const float *centroids, const void *bias, int bias_dtype, void *workspace,
+                          size_t workspace_bytes, cudaStream_t stream) {
+  OQ_CHECK_ARG(aligned16(x) && aligned16(packed), "x and packed weights must be 16-byte aligned");
+  OQ_CHECK_ARG(rows >= 1 && rows <= kSkMaxTokens, "the few-token kernel takes 1..128 rows");
+  EncodeTiledFn encode = encode_tiled_fn();
+  if (encode == nullptr) {
+    return fail(OQ_ERR_CUDA, "cuTensorMapEncodeTiled is not available from this driver");
+  }
+  int device = 0;
+  int sm_count = 0;
+  OQ_CHECK_CUDA(cudaGetDevice(&device));
+  OQ_CHECK_CUDA(cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, device));
+  const SkinnyPlan plan = skinny_plan(rows, in_features, out_features, sm_count > 256 ? 256 : sm_count);
+
+  CUtensorMap map_x;
+  CUtensorMap map_p;
+  {
+    const cuuint64_t dims[2] = {static_cast<cuuint64_t>(in_features), static_cast<cuuint64_t>(rows)};
+    const cuuint64_t strides[1] = {static_cast<cuuint64_t>(in_features) * 2};
+    const cuuint32_t box[2] = {kBK, static_cast<cuuint32_t>(plan.n_pad)};
+    const cuuint32_t elem[2] = {1, 1};
+    const CUresult rc = encode(&map_x, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<void *>(x),
+                               dims, strides, box, elem, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                               CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                               CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (rc != CUDA_SUCCESS) {
+      return fail(OQ_ERR_CUDA, "cuTensorMapEncodeTiled(activations) failed with code %d", (int)rc);
+    }
+  }
+  {
+    const int64_t row_bytes = in_features * bits / 8;
+    const bool by_tma = bits != 3;
+    const cuuint64_t dims[2] = {static_cast<cuuint64_t>(by_tma ? row_bytes : 16),
+                                static_cast<cuuint64_t>(by_tma ? out_features : 1)};
+    const cuuint64_t strides[1] = {static_cast<cuuint64_t>(by_tma ? row_bytes : 16)};
+    const cuuint32_t box[2] = {static_cast<cuuint32_t>(by_tma ? kBK * bits / 8 : 16),
+                               static_cast<cuuint32_t>(by_tma ? kSkRows : 1)};
+    const cuuint32_t elem[2] = {1, 1};
+    const CUresult rc = encode(&map_p, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<uint8_t *>(packed),
+                               dims, strides, box, elem, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                               CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                               CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (rc != CUDA_SUCCESS) {
+      return fail(OQ_ERR_CUDA, "cuTensorMapEncodeTiled(packed weights) failed with code %d", (int)rc);
+    }
+  }
+
+  SkinnyParams p{};
+  p.out = out;
+  p.packed = packed;
+  p.row_scale = row_scale;
+  p.table_scale = table_scale;
+  p.row_norms = static_cast<const __nv_bfloat16 *>(row_norms_bf16);
+  p.centroids = centroids;
+  p.bias = bias;
+  p.bias_dtype = bias == nullptr ? -1 : bias_dtype;
+  p.rows = static_cast<int>(rows);
+  p.out_features = out_features;
+  p.k_iters = static_cast<int>(in_features / kBK);
+  p.n_pad = plan.n_pad;
+  p.splits = plan.splits;
+  p.chunk_iters = plan.chunk_iters;
+  p.n_tiles = plan.n_tiles;
+  if (const char *skip = getenv("ORBIT_B200_DEBUG_SKIP")) {
+    p.debug_skip = atoi(skip);
+  }
+  if (plan.splits > 1) {
+    const size_t need = skinny_partial_bytes(plan, out_features);
+    if (workspace == nullptr || workspace_bytes < need) {
+      return fail(OQ_ERR_WORKSPACE, "workspace of %zu bytes given, %zu needed", workspace_bytes, need);
+    }
+    OQ_CHECK_ARG(aligned16(workspace), "workspace must be 16-byte aligned");
+    p.counters = static_cast<int *>(workspace);  // cleared by the kernel that ran just before
+    p.partial = reinterpret_cast<float *>(static_cast<unsigned char *>(workspace) + skinny_counter_bytes(plan));
+  }
+  int rc = OQ_OK;
+  switch (bits) {
+    case 2: rc = launch_skinny_bits<2>(map_x, map_p, p, sm_count, stream); break;
+    case 3: rc = launch_skinny_bits<3>(map_x, map_p, p, sm_count, stream); break;
+    case 4: rc = launch_skinny_bits<4>(map_x, map_p, p, sm_count, stream); break;
+    case 6: rc = launch_skinny_bits<6>(map_x, map_p, p, sm_count, stream); break;
+    default: rc = launch_skinny_bits<8>(map_x, map_p, p, sm_count, stream); break;
+  }
+  return rc;
 }
 
 int read_gemm_status(int *status) {

@@ -57,6 +57,8 @@ struct PrologueParams {
   const float *w_centroids;
   int w_bits;
   float *table_scale_out;
+  int *zero_words;   // cleared by CTA 0 (slice counters of the kernel that follows)
+  int zero_count;
 };
 
 // Number of boundaries strictly below `v` (sorted ascending, count = 2^bits - 1), as a
@@ -200,7 +202,11 @@ rotate_quantize_kernel(const PrologueParams p) {
   float *s_inv = s_norm + 8;     // [R] 1/(norm+eps)
   float *s_opscale = s_inv + 8;  // [R] 2^(14 - E) in f16 operand mode
 
+  // A kernel launched with programmatic stream serialization may start its own set-up now;
+  // it still waits (griddepcontrol.wait) for this grid to finish before it reads our output.
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   if (blockIdx.x == 0 && p.table_scale_out != nullptr) {
+    clear_words(p.zero_words, p.zero_count);
     search_table_scale(p.w_centroids, p.w_bits, p.table_scale_out, s_bnd);  // tables not filled yet
   }
   const int levels = 1 << p.bits;
@@ -448,7 +454,7 @@ int launch_rotate_quantize(const void *x, int x_dtype, int64_t rows, int64_t dim
                            const float *boundaries, const float *centroids, int bits, float eps,
                            void *x_q, uint8_t *codes, float *norms, float *f16_row_scale,
                            const float *w_centroids, int w_bits, float *table_scale_out,
-                           cudaStream_t stream) {
+                           int *zero_words, int zero_count, cudaStream_t stream) {
   OQ_CHECK_ARG(table_scale_out == nullptr || (w_centroids != nullptr && w_bits >= 1 && w_bits <= 8),
                "the table scale search needs the weight codebook");
   OQ_CHECK_ARG(f16_row_scale == nullptr || (x_dtype != OQ_DTYPE_F32 && x_q != nullptr),
@@ -530,6 +536,8 @@ int launch_rotate_quantize(const void *x, int x_dtype, int64_t rows, int64_t dim
   p.w_centroids = w_centroids;
   p.w_bits = w_bits;
   p.table_scale_out = table_scale_out;
+  p.zero_words = zero_words;
+  p.zero_count = zero_words != nullptr ? zero_count : 0;
 
   const int64_t ctas_needed = (rows + rows_per_cta - 1) / rows_per_cta;
   const int grid = static_cast<int>(std::min<int64_t>(ctas_needed, static_cast<int64_t>(sm_count) * 8));

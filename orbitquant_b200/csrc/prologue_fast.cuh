@@ -144,7 +144,9 @@ rotate_quantize_fast_kernel(const PrologueParams p) {
   float *s_opscale = s_inv + 8;                                                     // [8]
   uint16_t *s_outtab = reinterpret_cast<uint16_t *>(s_opscale + 8);                 // [R][kLevels]
 
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");  // see rotate_quantize_kernel
   if (blockIdx.x == 0 && p.table_scale_out != nullptr) {
+    clear_words(p.zero_words, p.zero_count);
     search_table_scale(p.w_centroids, p.w_bits, p.table_scale_out, rot);  // token buffers still free
   }
   for (int i = threadIdx.x; i < kLevels; i += kFastThreads) {

@@ -15,6 +15,14 @@ namespace oq {
 
 constexpr float kTableScaleBase = 256.0f;
 
+// The same CTA clears the few-token kernel's slice counters (one int per weight tile), which
+// live in the caller's workspace and so hold arbitrary bytes on entry.
+__device__ __forceinline__ void clear_words(int *words, int count) {
+  for (int i = threadIdx.x; i < count; i += blockDim.x) {
+    words[i] = 0;
+  }
+}
+
 // Called by all 256 threads of one CTA.  `scratch` holds at least 264 floats of shared memory.
 __device__ __forceinline__ void search_table_scale(const float *centroids, int bits, float *out,
                                                    float *scratch) {
