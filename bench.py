@@ -347,6 +347,13 @@ def run_decode(args, device, rank):
                                         out_features=m.out_features, in_features=m.in_features,
                                         bias=m.bias)
 
+    # layers of 3 MB and more take the few-token tcgen05 kernel (preceded here by the kernel
+    # that converts the caller's activations to its f16 operand), smaller ones the
+    # single-launch small-rows kernel
+    big = [n * k * w_bits // 8 >= 3 << 20 for _n, k, n, _g in specs]
+    decode_kernel_name = ("rows_to_f16_kernel + skinny_tcgen05_kernel" if all(big) else
+                          "small_rows_w4_kernel" if not any(big) else
+                          "small_rows_w4_kernel / rows_to_f16_kernel + skinny_tcgen05_kernel by layer size")
     kernel_graph = capture(matmul_only)
     kernel_ms = time_graph(kernel_graph, max(3, args.steps // sets)) / sets
     clocks = sampler.stop()
@@ -399,7 +406,7 @@ def run_decode(args, device, rank):
         "tflops": pass_flops / (cold_ms * 1e-3) / 1e12,
         "roofline": {"bound": "hbm", "achieved": kernel_gbs, "peak": peaks["hbm_gbs"], "unit": "GB/s",
                      "frac": kernel_gbs / peaks["hbm_gbs"], "traffic": NCU_TRAFFIC_BYTES.get(args.workload),
-                     "peak_source": peaks["source"], "kernel": "small_rows_w4_kernel",
+                     "peak_source": peaks["source"], "kernel": decode_kernel_name,
                      "avg_launch_us": kernel_ms * 1e3 / per_set, "launches_timed": per_set * sets},
         "e2e": {"value": pass_bytes / (e2e_ms * 1e-3) / 1e9, "unit": "GB/s",
                 "h2d_bytes_per_step": host_x.numel() * 2, "d2h_bytes_per_step": host_y.numel() * 2,

@@ -110,13 +110,17 @@ int choose_kernel(int kernel, int64_t rows, int64_t in_features, int64_t out_fea
   if (kernel != OQ_KERNEL_AUTO) {
     return kernel;
   }
-  if (rows <= 16 && small_rows_supported(rows, in_features, out_features, bits, dtype, mode)) {
-    // layers of a few megabytes and more stream through the tensor-core few-token kernel
-    if (use_skinny(rows, in_features, out_features, bits, dtype, mode) &&
-        out_features * in_features * bits / 8 >= (int64_t(3) << 20)) {
-      return OQ_KERNEL_TCGEN05;
-    }
+  const int64_t weight_bytes = out_features * in_features * bits / 8;
+  const bool skinny = use_skinny(rows, in_features, out_features, bits, dtype, mode);
+  if (rows <= 16 && small_rows_supported(rows, in_features, out_features, bits, dtype, mode) &&
+      (!skinny || weight_bytes < (int64_t(3) << 20))) {
+    // one launch, lowest latency; large layers in this mode stream through the persistent variant
     return OQ_KERNEL_SMALL_ROWS;
+  }
+  // few tokens on the tensor cores: any bit width, layers of a megabyte and more (below that
+  // the set-up of a tcgen05 kernel costs more than the general kernel's whole run)
+  if (skinny && (rows > 16 || weight_bytes >= (int64_t(1) << 20))) {
+    return OQ_KERNEL_TCGEN05;
   }
   if (rows > 16 && tcgen05_gemm_supported(rows, in_features, out_features, bits, dtype, mode)) {
     return OQ_KERNEL_TCGEN05;
