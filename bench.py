@@ -437,6 +437,8 @@ def main():
     parser.add_argument("--impl", default="ours", choices=["ours", "reference"])
     parser.add_argument("--workload", default="dit_block", choices=sorted(WORKLOADS))
     parser.add_argument("--no-cpu-baseline", action="store_true")
+    parser.add_argument("--gather", default="epilogue", choices=["epilogue", "nccl"],
+                        help="multi-GPU: how column shards are reassembled")
     parser.add_argument("--rows", type=int, default=0,
                         help="override the workload's token count (profiling on a smaller case)")
     args = parser.parse_args()
@@ -471,14 +473,28 @@ def main():
     inputs = [synth_activations(rows, k, WORKLOADS[args.workload][3] * 1000 + i).to(device)
               for i, (_n, k, _N, _g, _m) in enumerate(layers)]
 
+    # Column shards are reassembled either by the GEMM epilogue itself (each finished tile is
+    # stored into every rank's full-width buffer over NVLink; one inter-rank barrier follows)
+    # or, with --gather nccl, by an all-gather collective after the kernel.
+    fused_gather = distributed and args.gather == "epilogue" and rows > 128
+    peers = {}
+    if fused_gather:
+        from orbitquant_b200.sharding import PeerOutput
+        for i, (_name, _k, n, _g, _m) in enumerate(layers):
+            peers[i] = PeerOutput(rows, n, device)
+
+    def sharded_forward(i, x, want_full):
+        _name, _k, n, _g, module = layers[i]
+        if not (distributed and want_full):
+            return module(x)
+        if fused_gather:
+            peers[i].scatter(module, x)
+            peers[i].wait()
+            return peers[i].tensor
+        return gather_columns(module(x), n)
+
     def step():
-        outs = []
-        for (name, k, n, gather, module), x in zip(layers, inputs):
-            y = module(x)
-            if distributed and gather:
-                y = gather_columns(y, n)
-            outs.append(y)
-        return outs
+        return [sharded_forward(i, x, layers[i][3]) for i, x in enumerate(inputs)]
 
     def barrier():
         if distributed:
@@ -588,21 +604,13 @@ def main():
             dev_x[b].copy_(host_x, non_blocking=True)
             x_ready[b].record(copy_in)
         main.wait_event(x_ready[b])
-        qkv = layers[0][4](dev_x[b])
+        qkv = sharded_forward(0, dev_x[b], True)
         x_free[b].record(main)
-        if distributed:
-            qkv = gather_columns(qkv, layers[0][2])
         h = qkv[:, :layers[1][1]].contiguous()
-        h = layers[1][4](h)
-        if distributed:
-            h = gather_columns(h, layers[1][2])
-        h = layers[2][4](h)
-        if distributed:
-            h = gather_columns(h, layers[2][2])
+        h = sharded_forward(1, h, True)
+        h = sharded_forward(2, h, True)
         h = torch.nn.functional.gelu(h)
-        h = layers[3][4](h)
-        if distributed:
-            h = gather_columns(h, layers[3][2])
+        h = sharded_forward(3, h, True)
         done = torch.cuda.Event()
         done.record(main)
         with torch.cuda.stream(copy_out):
@@ -642,6 +650,8 @@ def main():
                              + ", ".join(f"{n_} {k}->{n}" for n_, k, n, _g, _m in layers)),
                 "l2": "per-step working set (inputs+weights+outputs) exceeds the 126 MB L2; no flush",
                 "parallelism": f"n_shard{world}" if distributed else "single",
+                "gather": ("gemm epilogue stores into every rank's buffer (peer memory), one barrier"
+                           if fused_gather else "nccl all_gather_into_tensor") if distributed else None,
                 "weight_mode": "centroid (f16 centroid operand, row norm in the epilogue)",
             },
             "roofline": roofline,

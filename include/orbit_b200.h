@@ -4,9 +4,10 @@
  * Every entry point takes plain device pointers, sizes and a CUDA stream
  * (a cudaStream_t passed as void*; NULL = the legacy default stream).  All pointers are
  * DEVICE pointers owned by the caller and must stay alive until the stream has run the
- * work.  Unless an entry point's comment says otherwise the library allocates nothing,
- * never synchronises the host with the device and keeps no device state of its own, so
- * every call may be captured into a CUDA graph.
+ * work.  Unless an entry point's comment says otherwise the library allocates nothing and
+ * never synchronises the host with the device, so every call may be captured into a CUDA
+ * graph.  Its only device state is the status word of the tensor-core kernels' bounded
+ * waits (oq_gemm_device_status) and the fixed scratch array of the no-allocation variant.
  *
  * Return value: 0 on success, a negative oq_status otherwise; oq_last_error() then holds
  * a message for the calling thread.  The host binding turns OQ_ERR_INVALID into the
@@ -184,6 +185,31 @@ int oq_linear_forward(void *out, const void *x, int dtype, int64_t rows, int64_t
 
 size_t oq_linear_workspace_bytes(int64_t rows, int64_t in_features, int64_t out_features,
                                  int weight_bits, int dtype, int weight_mode, int kernel);
+
+/* ---- column-sharded layers: forward with the all-gather in the epilogue ----------------- */
+
+/* oq_linear_forward whose result tile is stored into EVERY one of `n_outs` (1..8) row-major
+ * bf16 buffers, each [rows, out_ld] with this call's columns starting at `out_col`.  A layer
+ * sharded along its output features over several GPUs passes its own full-width buffer and
+ * the peer-mapped address of the same buffer on every other GPU (symmetric memory / CUDA
+ * IPC): the kernel's epilogue stores each finished tile over NVLink while the next tiles are
+ * still being computed, and no all-gather collective follows.  The caller synchronises the
+ * ranks afterwards (every peer's stores must have landed before a rank reads its buffer).
+ * The reference has no multi-GPU path for this operator; its closest counterpart is the
+ * torch.distributed all-gather a caller would run on the column shards
+ * (orbitquant_b200/sharding.py: gather_columns).  Exists in the large-row tcgen05 kernel
+ * only: bf16, rows > 128, in_features % 64 == 0, centroid weight arithmetic; other
+ * problems return OQ_ERR_UNSUPPORTED.  out_ld, out_col and out_features multiples of 8
+ * keep the stores 16 bytes wide.  Workspace: oq_linear_workspace_bytes(..., OQ_KERNEL_TCGEN05). */
+int oq_linear_forward_scatter(void *const *outs, int n_outs, int64_t out_ld, int64_t out_col,
+                              const void *x, int dtype, int64_t rows, int64_t in_features,
+                              int64_t out_features, const uint8_t *packed, int64_t packed_bytes,
+                              int weight_bits, const void *row_norms_bf16,
+                              const float *weight_centroids, const void *bias, int bias_dtype,
+                              const int32_t *perm, const int8_t *signs, int64_t block,
+                              const float *act_boundaries, const float *act_centroids,
+                              int act_bits, float eps, void *workspace, size_t workspace_bytes,
+                              void *stream);
 
 /* ---- no-allocation variant ------------------------------------------------------------ */
 

@@ -66,6 +66,12 @@ int launch_tcgen05_skinny(void *out, const void *x_f16, const float *row_scale,
                           const void *row_norms_bf16, const float *centroids, const void *bias,
                           int bias_dtype, void *workspace, size_t workspace_bytes,
                           cudaStream_t stream);
+int launch_tcgen05_gemm_scatter(void *const *outs, int n_outs, int64_t out_ld, int64_t out_col,
+                                const void *x_f16, const float *row_scale, const float *table_scale,
+                                int64_t rows, int64_t in_features, int64_t out_features,
+                                const uint8_t *packed, int bits, const void *row_norms_bf16,
+                                const float *centroids, const void *bias, int bias_dtype,
+                                cudaStream_t stream);
 int read_gemm_status(int *status);
 int clear_gemm_status();
 
@@ -477,6 +483,55 @@ int oq_linear_forward(void *out, const void *x, int dtype, int64_t rows, int64_t
                                  bias_dtype, weight_mode, chosen,
                                  static_cast<unsigned char *>(workspace) + xq_bytes,
                                  workspace_bytes - xq_bytes, stream);
+}
+
+int oq_linear_forward_scatter(void *const *outs, int n_outs, int64_t out_ld, int64_t out_col,
+                              const void *x, int dtype, int64_t rows, int64_t in_features,
+                              int64_t out_features, const uint8_t *packed, int64_t packed_bytes,
+                              int weight_bits, const void *row_norms_bf16,
+                              const float *weight_centroids, const void *bias, int bias_dtype,
+                              const int32_t *perm, const int8_t *signs, int64_t block,
+                              const float *act_boundaries, const float *act_centroids,
+                              int act_bits, float eps, void *workspace, size_t workspace_bytes,
+                              void *stream) {
+  OQ_CHECK_ARG(outs != nullptr, "null output list");
+  OQ_CHECK_ARG(valid_dtype(dtype), "x must be float32, float16, or bfloat16");
+  OQ_CHECK_ARG(rows >= 0 && in_features > 0 && out_features >= 0, "negative or empty shape");
+  OQ_CHECK_ARG(weight_bits >= 1 && weight_bits <= 8, "bits must be in [1, 8]");
+  const int64_t needed = (out_features * in_features * weight_bits + 7) / 8;
+  OQ_CHECK_ARG(packed_bytes >= needed, "packed weights are too short");
+  if (rows == 0 || out_features == 0) {
+    return OQ_OK;
+  }
+  if (int rc = check_device()) {
+    return rc;
+  }
+  const int mode = OQ_WEIGHT_CENTROID;
+  if (!tcgen05_gemm_supported(rows, in_features, out_features, weight_bits, dtype, mode) ||
+      use_skinny(rows, in_features, out_features, weight_bits, dtype, mode)) {
+    return fail(OQ_ERR_UNSUPPORTED,
+                "the multi-destination epilogue exists in the large-row tcgen05 kernel only "
+                "(bf16, more than 128 rows, in_features %% 64 == 0)");
+  }
+  const size_t need = tcgen05_head_bytes(rows, in_features);
+  if (workspace == nullptr || workspace_bytes < need) {
+    return fail(OQ_ERR_WORKSPACE, "workspace of %zu bytes given, %zu needed", workspace_bytes, need);
+  }
+  OQ_CHECK_ARG(aligned16(workspace), "workspace must be 16-byte aligned");
+  OQ_CHECK_ARG(packed && row_norms_bf16 && weight_centroids, "null device pointer");
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  float *row_scale = reinterpret_cast<float *>(static_cast<unsigned char *>(workspace) +
+                                               f16_operand_bytes(rows, in_features));
+  float *table_scale = row_scale + rows;
+  if (int rc = launch_rotate_quantize(x, dtype, rows, in_features, perm, signs, block, act_boundaries,
+                                      act_centroids, act_bits, eps, workspace, nullptr, nullptr,
+                                      row_scale, weight_centroids, weight_bits, table_scale, nullptr,
+                                      0, s)) {
+    return rc;
+  }
+  return launch_tcgen05_gemm_scatter(outs, n_outs, out_ld, out_col, workspace, row_scale, table_scale,
+                                     rows, in_features, out_features, packed, weight_bits,
+                                     row_norms_bf16, weight_centroids, bias, bias_dtype, s);
 }
 
 // Status word of the tcgen05 kernel's bounded waits (0 = every wait completed).  Reading

@@ -82,8 +82,17 @@ struct Tile {
   static constexpr int kThreads = (kExpanderWarps + 2) * 32;
 };
 
+constexpr int kMaxOutputs = 8;
+
 struct GemmParams {
-  void *out;
+  // The result tile is stored into every one of `n_outs` row-major buffers (leading dimension
+  // `out_ld` elements, first column `out_col`): the caller's own buffer and, in a
+  // column-sharded layer, the same buffer on each peer GPU -- the all-gather of the shards
+  // happens in the epilogue, tile by tile, instead of in a collective afterwards.
+  void *outs[kMaxOutputs];
+  int n_outs;
+  int64_t out_ld;
+  int64_t out_col;
   const uint8_t *packed;   // the bit stream (read directly only by the 3-bit expanders)
   const float *row_scale;  // per token: factor the f16 activations were divided by
   const float *table_scale;  // scale of the f16 weight table (NULL: 2^8)
@@ -607,43 +616,68 @@ gemm_w4_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
     }
 
     // ---- epilogue: warp w reads accumulator w/4, TMEM lanes 32*(w%4).. ----
+    // A lane of tcgen05.ld holds one output ROW, so storing from registers would write 32
+    // scattered 16-byte pieces per instruction.  The warp instead parks its 32 x BN bf16 tile
+    // in the (now idle) pipeline stages and writes it out row by row: one instruction = one
+    // contiguous run of BN*2 bytes, which is what both L2 and -- for a peer GPU's buffer --
+    // NVLink want.  The row pitch is padded by 16 bytes so that the row-per-lane writes hit
+    // all banks.
+    constexpr int kPitch = BN * 2 + 16;
+    static_assert(kEpilogueWarps * 32 * kPitch <= T::kStages * T::kStageBytes, "epilogue staging space");
     if (ok && warp < kEpilogueWarps && mbar_wait(acc_full_bar, 0, s_abort, 5)) {
       tc_fence_after();
       const int half = warp >> 2;
       const int quarter = warp & 3;
-      const int64_t m = m0 + half * 128 + quarter * 32 + lane;
+      const int64_t m_first = m0 + half * 128 + quarter * 32;
+      const int64_t m = m_first + lane;
       const float row_scale = m < p.rows ? p.row_scale[m] : 0.0f;
-      const bool vec_ok = (p.out_features % 8) == 0;
-      __nv_bfloat16 *out_row = static_cast<__nv_bfloat16 *>(p.out) + m * p.out_features;
+      unsigned char *park = stage_ptr + warp * (32 * kPitch);
 #pragma unroll 1
       for (int c0 = 0; c0 < BN; c0 += 32) {
         uint32_t v[32];
         tmem_ld_32x32b_x32(tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + half * BN + c0, v);
         tmem_ld_wait();
-        if (m < p.rows) {
-          uint32_t packed[16];
+        uint4 *dst = reinterpret_cast<uint4 *>(park + lane * kPitch + c0 * 2);
 #pragma unroll
-          for (int j = 0; j < 16; ++j) {
+        for (int q = 0; q < 4; ++q) {
+          uint32_t w[4];
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            const int j = 4 * q + e;
             const float a = fmaf(__uint_as_float(v[2 * j]), row_scale * s_scale[c0 + 2 * j],
                                  s_bias[c0 + 2 * j]);
             const float b = fmaf(__uint_as_float(v[2 * j + 1]), row_scale * s_scale[c0 + 2 * j + 1],
                                  s_bias[c0 + 2 * j + 1]);
             const __nv_bfloat162 h = __floats2bfloat162_rn(a, b);
-            packed[j] = *reinterpret_cast<const uint32_t *>(&h);
+            w[e] = *reinterpret_cast<const uint32_t *>(&h);
           }
-          const int64_t n = n0 + c0;
-          if (vec_ok && n + 32 <= p.out_features) {
-            uint4 *dst = reinterpret_cast<uint4 *>(out_row + n);
-#pragma unroll
-            for (int q = 0; q < 4; ++q) {
-              dst[q] = make_uint4(packed[4 * q], packed[4 * q + 1], packed[4 * q + 2], packed[4 * q + 3]);
-            }
+          dst[q] = make_uint4(w[0], w[1], w[2], w[3]);
+        }
+      }
+      __syncwarp();
+      // lane l carries columns 8l .. 8l+7 of every row
+      const bool vec_ok = (p.out_features % 8) == 0 && (p.out_ld % 8) == 0 && (p.out_col % 8) == 0;
+      const int64_t n = n0 + lane * 8;
+      const bool lane_in_tile = lane * 8 < BN;
+      const bool lane_full = lane_in_tile && n + 8 <= p.out_features;
+      const int64_t rows_here = p.rows - m_first < 32 ? p.rows - m_first : 32;
+      for (int d = 0; d < p.n_outs; ++d) {
+        __nv_bfloat16 *out = static_cast<__nv_bfloat16 *>(p.outs[d]) + p.out_col + n;
+#pragma unroll 4
+        for (int r = 0; r < rows_here; ++r) {
+          if (!lane_in_tile) {
+            continue;
+          }
+          const uint4 val = *reinterpret_cast<const uint4 *>(park + r * kPitch + lane * 16);
+          __nv_bfloat16 *dst = out + (m_first + r) * p.out_ld;
+          if (vec_ok && lane_full) {
+            *reinterpret_cast<uint4 *>(dst) = val;
           } else {
+            const uint32_t w[4] = {val.x, val.y, val.z, val.w};
 #pragma unroll
-            for (int j = 0; j < 32; ++j) {
+            for (int j = 0; j < 8; ++j) {
               if (n + j < p.out_features) {
-                const uint16_t bits = static_cast<uint16_t>(packed[j >> 1] >> ((j & 1) * 16));
-                reinterpret_cast<uint16_t *>(out_row)[n + j] = bits;
+                reinterpret_cast<uint16_t *>(dst)[j] = static_cast<uint16_t>(w[j >> 1] >> ((j & 1) * 16));
               }
             }
           }
@@ -811,12 +845,37 @@ int launch_bits(int bn, const CUtensorMap &map_a, const CUtensorMap &map_p, cons
   }
 }
 
+int launch_tcgen05_gemm_scatter(void *const *outs, int n_outs, int64_t out_ld, int64_t out_col,
+                                const void *x, const float *row_scale, const float *table_scale,
+                                int64_t rows, int64_t in_features, int64_t out_features,
+                                const uint8_t *packed, int bits, const void *row_norms_bf16,
+                                const float *centroids, const void *bias, int bias_dtype,
+                                cudaStream_t stream);
+
 int launch_tcgen05_gemm(void *out, const void *x, const float *row_scale, const float *table_scale,
                         int64_t rows, int64_t in_features, int64_t out_features, const uint8_t *packed, int bits,
                         const void *row_norms_bf16, const float *centroids, const void *bias,
                         int bias_dtype, cudaStream_t stream) {
-  OQ_CHECK_ARG(aligned16(x) && aligned16(packed) && aligned16(out),
-               "x, packed weights and out must be 16-byte aligned for the tcgen05 kernel");
+  void *outs[1] = {out};
+  return launch_tcgen05_gemm_scatter(outs, 1, out_features, 0, x, row_scale, table_scale, rows,
+                                     in_features, out_features, packed, bits, row_norms_bf16,
+                                     centroids, bias, bias_dtype, stream);
+}
+
+int launch_tcgen05_gemm_scatter(void *const *outs, int n_outs, int64_t out_ld, int64_t out_col,
+                                const void *x, const float *row_scale, const float *table_scale,
+                                int64_t rows, int64_t in_features, int64_t out_features,
+                                const uint8_t *packed, int bits, const void *row_norms_bf16,
+                                const float *centroids, const void *bias, int bias_dtype,
+                                cudaStream_t stream) {
+  OQ_CHECK_ARG(n_outs >= 1 && n_outs <= kMaxOutputs, "1 to %d output buffers", kMaxOutputs);
+  OQ_CHECK_ARG(out_col >= 0 && out_ld >= out_col + out_features,
+               "the column range does not fit the leading dimension");
+  for (int d = 0; d < n_outs; ++d) {
+    OQ_CHECK_ARG(outs[d] != nullptr && aligned16(outs[d]), "output buffers must be 16-byte aligned");
+  }
+  OQ_CHECK_ARG(aligned16(x) && aligned16(packed),
+               "x and packed weights must be 16-byte aligned for the tcgen05 kernel");
   EncodeTiledFn encode = encode_tiled_fn();
   if (encode == nullptr) {
     return fail(OQ_ERR_CUDA, "cuTensorMapEncodeTiled is not available from this driver");
@@ -893,7 +952,12 @@ int launch_tcgen05_gemm(void *out, const void *x, const float *row_scale, const 
   }
 
   GemmParams p{};
-  p.out = out;
+  for (int d = 0; d < n_outs; ++d) {
+    p.outs[d] = outs[d];
+  }
+  p.n_outs = n_outs;
+  p.out_ld = out_ld;
+  p.out_col = out_col;
   p.packed = packed;
   p.row_scale = row_scale;
   p.table_scale = table_scale;

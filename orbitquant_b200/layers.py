@@ -315,6 +315,31 @@ class OrbitQuantLinear(nn.Module):
             weight_mode=native.WEIGHT_MODE_NAMES[self.weight_mode],
             kernel=native.KERNEL_NAMES[self.kernel])
 
+    def forward_scatter(self, x: torch.Tensor, out_ptrs, out_ld: int, out_col: int) -> None:
+        """Forward of a column shard whose result goes straight into every buffer of
+        ``out_ptrs`` (device addresses of row-major bf16 ``[rows, out_ld]`` buffers, this
+        rank's and its peers') at columns ``out_col .. out_col + out_features``.  See
+        ``orbitquant_b200.sharding.PeerOutput``."""
+        if x.device.type != "cuda":
+            raise RuntimeError("OrbitQuantLinear (orbitquant_b200) requires CUDA input tensors")
+        if x.shape[-1] != self.in_features:
+            raise ValueError(f"expected last dimension {self.in_features}, got {x.shape[-1]}")
+        device = x.device
+        self._ensure_derived_constants(device)
+        packed = self.packed_weight_indices
+        if packed.device != device or packed.dtype != torch.uint8 or not packed.is_contiguous():
+            raise RuntimeError("move the module to the input's device first")
+        native.linear_forward_scatter(
+            x, packed, self._row_norms_for(device), self._bias_for(device),
+            out_ptrs=out_ptrs, out_ld=out_ld, out_col=out_col,
+            permutation=self._rotation_permutation, signs=self._rotation_signs,
+            block_size=self.rotation.block_size,
+            act_boundaries=self._activation_codebook_boundaries,
+            act_centroids=self._activation_codebook_centroids,
+            weight_centroids=self._weight_codebook_centroids,
+            weight_bits=self.weight_bits, out_features=self.out_features,
+            eps=self.activation_eps)
+
     def dequantize_weight(self, dtype: torch.dtype = torch.bfloat16) -> torch.Tensor:
         """Dense ``row_norm[n] * centroid[idx[n,k]]`` in the ROTATED basis
         (``layers.py:1060-1070``)."""

@@ -48,6 +48,9 @@ _SIGNATURES = {
     "oq_linear_forward_static": (_int, [_vp, _vp, _int, _i64, _i64, _i64, _vp, _i64, _int, _vp, _vp,
                                         _vp, _int, _vp, _vp, _i64, _vp, _vp, _int, _f32, _int, _int,
                                         _vp]),
+    "oq_linear_forward_scatter": (_int, [_vp, _int, _i64, _i64, _vp, _int, _i64, _i64, _i64, _vp, _i64,
+                                         _int, _vp, _vp, _vp, _int, _vp, _vp, _i64, _vp, _vp, _int,
+                                         _f32, _vp, _sz, _vp]),
     "oq_static_scratch_bytes": (_sz, []),
     "oq_linear_workspace_bytes": (_sz, [_i64, _i64, _i64, _int, _int, _int, _int]),
     "oq_gemm_device_status": (_int, [ctypes.POINTER(ctypes.c_int)]),
@@ -313,3 +316,35 @@ def linear_forward(x, packed, row_norms, bias, *, permutation, signs, block_size
     if out_dtype is not None and out_dtype != result.dtype:
         result = result.to(out_dtype)
     return result
+
+
+def linear_forward_scatter(x, packed, row_norms, bias, *, out_ptrs, out_ld, out_col, permutation,
+                           signs, block_size, act_boundaries, act_centroids, weight_centroids,
+                           weight_bits, out_features, eps):
+    """The whole forward of a column shard, its result stored into every buffer of
+    ``out_ptrs`` (device addresses of row-major bf16 ``[rows, out_ld]`` buffers: this rank's
+    and its peers' mapped copies) at columns ``out_col ..``.  Nothing is returned; the caller
+    synchronises the ranks before reading.  Raises RuntimeError where the large-row
+    tcgen05 kernel does not apply."""
+    _require_cuda("x", x)
+    if x.dtype not in DTYPE_CODES:
+        raise ValueError("x must be float32, float16, or bfloat16")
+    in_features = x.shape[-1]
+    device = x.device
+    x2 = x.contiguous().reshape(-1, in_features)
+    rows = x2.shape[0]
+    act_bits = int(act_centroids.numel()).bit_length() - 1
+    code = DTYPE_CODES[x.dtype]
+    lib = load()
+    ws_bytes = lib.oq_linear_workspace_bytes(rows, in_features, out_features, weight_bits, code,
+                                             WEIGHT_AUTO, KERNEL_TCGEN05)
+    ws = torch.empty(max(ws_bytes, 16), dtype=torch.uint8, device=device)
+    bias_code = 0 if bias is None else DTYPE_CODES[bias.dtype]
+    ptr_array = (ctypes.c_void_p * len(out_ptrs))(*[int(p) for p in out_ptrs])
+    with torch.cuda.device(device):
+        _check(lib.oq_linear_forward_scatter(
+            ptr_array, len(out_ptrs), int(out_ld), int(out_col), _ptr(x2), code, rows, in_features,
+            out_features, _ptr(packed), packed.numel(), weight_bits, _ptr(row_norms),
+            _ptr(weight_centroids), _ptr(bias), bias_code, _ptr(permutation), _ptr(signs),
+            int(block_size), _ptr(act_boundaries), _ptr(act_centroids), act_bits, float(eps),
+            _ptr(ws), ws_bytes, _stream(device)))

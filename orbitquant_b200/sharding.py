@@ -91,3 +91,41 @@ def gather_columns(y_local: torch.Tensor, out_features: int, group=None) -> torc
     else:
         full = torch.cat([gathered[r, :, :widths[r]] for r in range(world)], dim=-1)
     return full.reshape(*lead, out_features)
+
+
+class PeerOutput:
+    """Full-width ``[rows, out_features]`` bf16 output of a column-sharded layer, allocated in
+    symmetric memory so that every rank holds the peer-mapped address of every other rank's
+    copy.  ``scatter(module, x)`` runs the rank's shard with the all-gather folded into the
+    GEMM epilogue (each finished tile is stored into all ranks' copies over NVLink);
+    ``wait()`` is the inter-rank barrier after which ``tensor`` holds every shard.
+
+    Plain peer stores only: no multicast object is created, so a rank that dies does not
+    take the others' NVLink down with it."""
+
+    def __init__(self, rows: int, out_features: int, device, group=None):
+        import os
+
+        # peer loads/stores only; no NVLink multicast object is bound to the buffer
+        os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")
+        import torch.distributed._symmetric_memory as symm_mem
+
+        self.group = group if group is not None else dist.group.WORLD
+        self.world = dist.get_world_size(self.group)
+        self.rank = dist.get_rank(self.group)
+        self.out_features = out_features
+        self.tensor = symm_mem.empty((rows, out_features), dtype=torch.bfloat16, device=device)
+        self.handle = symm_mem.rendezvous(self.tensor, self.group)
+        # own copy first: the local store is the one the next layer reads soonest
+        order = [self.rank] + [r for r in range(self.world) if r != self.rank]
+        self.ptrs = [int(self.handle.buffer_ptrs[r]) for r in order]
+        self.lo, self.hi = shard_bounds(out_features, self.world, self.rank)
+
+    def scatter(self, module, x: torch.Tensor) -> None:
+        if module.out_features != self.hi - self.lo:
+            raise ValueError("module is not this rank's column shard of the output")
+        module.forward_scatter(x, self.ptrs, self.out_features, self.lo)
+
+    def wait(self) -> None:
+        """Every rank's stores into this rank's copy have landed (and this rank's into theirs)."""
+        self.handle.barrier()
