@@ -51,6 +51,11 @@ constexpr int kBK = 64;
 constexpr int kEpilogueWarps = 8;  // two accumulators x four TMEM lane quarters
 constexpr float kCentroidScale = kTableScaleBase;  // table scale when none was searched
 constexpr uint32_t kSpinLimit = 1u << 22;
+// Rate of the CTA-pair kernel relative to the 256-wide single-CTA tile.  Measured 0.89 (fc1
+// 3072->12288 at 4608 rows: 1040 against 1164 TFLOP/s): halving the decode does not pay
+// because the tensor pipe is held back by shared-memory operand reads, which a pair does not
+// reduce, and the pair adds a cross-CTA hop to every stage hand-over.  0 keeps it opt-in.
+constexpr double kPairRate = 0.0;
 
 template <int BN, int BITS>
 struct Tile {
@@ -413,6 +418,9 @@ gemm_w4_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
     s_cent[i] = p.centroids[i];
   }
   __syncthreads();
+  // The launch allows this grid to become resident while the kernel before it in the stream
+  // (the prologue) is still running; everything below reads that kernel's output.
+  asm volatile("griddepcontrol.wait;" ::: "memory");
   // chosen by the kernel that ran just before this one (table_scale.cuh); 2^8 without it
   const float table_scale = p.table_scale != nullptr ? __ldg(p.table_scale) : kCentroidScale;
   if (BITS == 6) {  // [entry][32 lane copies]
@@ -797,12 +805,24 @@ int launch_bn(const CUtensorMap &map_a, const CUtensorMap &map_p, const GemmPara
                                        Tile<BN, BITS>::kSmemBytes);
   });
   OQ_CHECK_CUDA(attr_status);
-  gemm_w4_tcgen05_kernel<BN, BITS><<<grid, Tile<BN, BITS>::kThreads, Tile<BN, BITS>::kSmemBytes, stream>>>(map_a, map_p, p);
-  OQ_CHECK_CUDA(cudaGetLastError());
+  // Programmatic stream serialization: CTAs may take over SMs as the prologue's last wave
+  // drains (set-up, tensor-memory allocation); griddepcontrol.wait orders the dependent reads.
+  cudaLaunchConfig_t config = {};
+  config.gridDim = dim3(grid);
+  config.blockDim = dim3(Tile<BN, BITS>::kThreads);
+  config.dynamicSmemBytes = Tile<BN, BITS>::kSmemBytes;
+  config.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  config.attrs = attr;
+  config.numAttrs = 1;
+  OQ_CHECK_CUDA(cudaLaunchKernelEx(&config, gemm_w4_tcgen05_kernel<BN, BITS>, map_a, map_p, p));
   count_launch();
   return OQ_OK;
 }
 
+#include "gemm_pair_tcgen05.cuh"
 #include "skinny_tcgen05.cuh"
 
 }  // namespace
@@ -913,8 +933,32 @@ int launch_tcgen05_gemm_scatter(void *const *outs, int n_outs, int64_t out_ld, i
       bn = value;
     }
   }
+  // A pair of CTAs (cta_group::2) on a 512 x 256 tile halves the decode work per MMA; it
+  // wins when its grid fills the machine about as well.  ORBIT_B200_PAIR=0 / 1 pins the choice.
+  const int64_t m_pairs = (rows + 2 * kBM - 1) / (2 * kBM);
+  const int64_t pair_tiles = m_pairs * ((out_features + 255) / 256);
+  bool use_pair = false;
+  {
+    const int64_t ctas = 2 * pair_tiles;
+    const int64_t waves = (ctas + sm_count - 1) / sm_count;
+    const double useful_n = static_cast<double>(out_features) /
+                            static_cast<double>(((out_features + 255) / 256) * 256);
+    const double useful_m = static_cast<double>(rows) / static_cast<double>(m_pairs * 2 * kBM);
+    const double single_useful_m = static_cast<double>(rows) / static_cast<double>(m_tiles * kBM);
+    const double pair_score = kPairRate * useful_n * useful_m * static_cast<double>(ctas) /
+                              static_cast<double>(waves * sm_count);
+    const double single_score = std::max(best, score(bn, bn == 256 ? 1.0 : (bn == 192 ? 0.93 : 0.76))) *
+                                single_useful_m;
+    use_pair = pair_score > single_score;
+  }
+  if (const char *forced = getenv("ORBIT_B200_PAIR")) {
+    use_pair = atoi(forced) != 0;
+  }
+  if (use_pair) {
+    bn = 128;  // the packed tensor map's box: the 128 weight rows one CTA of the pair expands
+  }
   const int64_t n_tiles = (out_features + bn - 1) / bn;
-  OQ_CHECK_ARG(m_tiles * n_tiles < (1ll << 31), "too many output tiles");
+  OQ_CHECK_ARG(m_tiles * n_tiles < (1ll << 31) && pair_tiles < (1ll << 30), "too many output tiles");
 
   CUtensorMap map_a;
   CUtensorMap map_p;
@@ -971,6 +1015,17 @@ int launch_tcgen05_gemm_scatter(void *const *outs, int n_outs, int64_t out_ld, i
   p.m_tiles = static_cast<int>(m_tiles);
   if (const char *skip = getenv("ORBIT_B200_DEBUG_SKIP")) {
     p.debug_skip = atoi(skip);
+  }
+  if (use_pair) {
+    p.m_tiles = static_cast<int>(m_pairs);
+    const int pairs = static_cast<int>(pair_tiles);
+    switch (bits) {
+      case 2: return launch_pair_bits<2>(map_a, map_p, p, pairs, stream);
+      case 3: return launch_pair_bits<3>(map_a, map_p, p, pairs, stream);
+      case 4: return launch_pair_bits<4>(map_a, map_p, p, pairs, stream);
+      case 6: return launch_pair_bits<6>(map_a, map_p, p, pairs, stream);
+      default: return launch_pair_bits<8>(map_a, map_p, p, pairs, stream);
+    }
   }
   const int grid = static_cast<int>(m_tiles * n_tiles);
   switch (bits) {

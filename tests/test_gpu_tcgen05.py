@@ -190,3 +190,24 @@ def test_module_auto_dispatch_uses_tcgen05(oracle):
         act_centroids=module.activation_codebook.centroids,
         w_centroids=module.weight_codebook.centroids, w_bits=4, out_features=512)
     _check_close(y, ref, "module W4A4 config-1 slice")
+
+
+@pytest.mark.parametrize("bits,rows,k,n", [(4, 300, 64, 256), (4, 1100, 1024, 1152), (2, 600, 768, 456),
+                                           (3, 600, 768, 456), (6, 520, 512, 264), (8, 520, 256, 520)])
+def test_cta_pair_kernel_equals_single_cta_kernel(golden_codebooks, bits, rows, k, n, monkeypatch):
+    """The cta_group::2 variant (a pair of CTAs shares every expanded weight tile; selected
+    with ORBIT_B200_PAIR=1, off by default because it measured slower) issues the same f16
+    products and accumulates them in the same order, so it must agree bit for bit."""
+    from conftest import codebook_from_golden
+    dev = _dev()
+    idx, packed, rn, bias = _random_layer(k, n, bits, seed=bits + rows)
+    cent = (codebook_from_golden(golden_codebooks, 256, 8) if bits == 8 else get_codebook(k, bits)).centroids
+    x = (torch.randn(rows, k) * 0.9).to(torch.bfloat16).to(dev)
+    args = dict(bits=bits, out_features=n, in_features=k, bias=bias, kernel=native.KERNEL_TCGEN05)
+    native.gemm_clear_device_status()
+    monkeypatch.setenv("ORBIT_B200_PAIR", "0")
+    single = native.matmul_packed_weight(x, packed.to(dev), rn, cent, **args)
+    monkeypatch.setenv("ORBIT_B200_PAIR", "1")
+    pair = native.matmul_packed_weight(x, packed.to(dev), rn, cent, **args)
+    _assert_status_clean()
+    assert torch.equal(single, pair)
