@@ -186,6 +186,26 @@ int oq_linear_forward(void *out, const void *x, int dtype, int64_t rows, int64_t
 size_t oq_linear_workspace_bytes(int64_t rows, int64_t in_features, int64_t out_features,
                                  int weight_bits, int dtype, int weight_mode, int kernel);
 
+/* ---- offline weight quantise-and-pack --------------------------------------------------- */
+
+/* W [out_features, in_features] (row-major, any of the three dtypes) -> the packed index
+ * stream and the bf16 row norms a layer stores.  Replaces the reference's weight path
+ * (src/orbitquant/layers.py:102-222; on CUDA its Triton kernels, triton_cuda.py:2849-2935):
+ * index = bucketize( (fwht(W[n, perm] * signs) * 1/sqrt(block)) / max(norm_n, eps) ), packed
+ * little-endian.  With `row_norms_in` (f32 [out_features]) the indices are bit-identical to
+ * the reference's torch CPU expression evaluated with those norms; with NULL the norms are
+ * computed here (double accumulation, rounded once to f32), which may differ from a given
+ * fp32 reduction order in the last bit.  `centroids` is the codebook's table (unused by the
+ * indices; kept for a uniform interface).  Workspace: oq_quantize_weight_workspace_bytes
+ * (one byte per weight + the f32 norms). */
+int oq_quantize_weight(const void *weight, int dtype, int64_t out_features, int64_t in_features,
+                       const int32_t *perm, const int8_t *signs, int64_t block,
+                       const float *boundaries, const float *centroids, int bits, float eps,
+                       const float *row_norms_in, void *row_norms_bf16_out, uint8_t *packed_out,
+                       void *workspace, size_t workspace_bytes, void *stream);
+
+size_t oq_quantize_weight_workspace_bytes(int64_t out_features, int64_t in_features);
+
 /* ---- column-sharded layers: forward with the all-gather in the epilogue ----------------- */
 
 /* oq_linear_forward whose result tile is stored into EVERY one of `n_outs` (1..8) row-major

@@ -22,7 +22,11 @@ int launch_rotate_quantize(const void *x, int x_dtype, int64_t rows, int64_t dim
                            const float *boundaries, const float *centroids, int bits, float eps,
                            void *x_q, uint8_t *codes, float *norms, float *f16_row_scale,
                            const float *w_centroids, int w_bits, float *table_scale_out,
-                           int *zero_words, int zero_count, cudaStream_t stream);
+                           int *zero_words, int zero_count, cudaStream_t stream,
+                           const float *given_norms = nullptr);
+int launch_weight_row_norms(const void *w, int dtype, int64_t rows, int64_t dim, float *norms_f32,
+                            void *norms_bf16, cudaStream_t stream);
+int launch_norms_to_bf16(const float *norms, int64_t rows, void *out, cudaStream_t stream);
 int launch_tiled_matmul(void *out, const void *x, int dtype, int64_t rows, int64_t in_features,
                         int64_t out_features, const uint8_t *packed, int bits,
                         const void *row_norms_bf16, const float *centroids, const void *bias,
@@ -532,6 +536,56 @@ int oq_linear_forward_scatter(void *const *outs, int n_outs, int64_t out_ld, int
   return launch_tcgen05_gemm_scatter(outs, n_outs, out_ld, out_col, workspace, row_scale, table_scale,
                                      rows, in_features, out_features, packed, weight_bits,
                                      row_norms_bf16, weight_centroids, bias, bias_dtype, s);
+}
+
+size_t oq_quantize_weight_workspace_bytes(int64_t out_features, int64_t in_features) {
+  if (out_features <= 0 || in_features <= 0) {
+    return 0;
+  }
+  return align_up(static_cast<size_t>(out_features) * in_features, 256) +
+         align_up(static_cast<size_t>(out_features) * 4, 256);
+}
+
+int oq_quantize_weight(const void *weight, int dtype, int64_t out_features, int64_t in_features,
+                       const int32_t *perm, const int8_t *signs, int64_t block,
+                       const float *boundaries, const float *centroids, int bits, float eps,
+                       const float *row_norms_in, void *row_norms_bf16_out, uint8_t *packed_out,
+                       void *workspace, size_t workspace_bytes, void *stream) {
+  OQ_CHECK_ARG(bits >= 1 && bits <= 8, "bits must be in [1, 8]");
+  OQ_CHECK_ARG(valid_dtype(dtype), "weight must be float32, float16, or bfloat16");
+  OQ_CHECK_ARG(out_features >= 0 && in_features > 0, "negative or empty shape");
+  if (out_features == 0) {
+    return OQ_OK;
+  }
+  OQ_CHECK_ARG(weight && row_norms_bf16_out && packed_out, "null device pointer");
+  const size_t need = oq_quantize_weight_workspace_bytes(out_features, in_features);
+  if (workspace == nullptr || workspace_bytes < need) {
+    return fail(OQ_ERR_WORKSPACE, "workspace of %zu bytes given, %zu needed", workspace_bytes, need);
+  }
+  OQ_CHECK_ARG(aligned16(workspace), "workspace must be 16-byte aligned");
+  if (int rc = check_device()) {
+    return rc;
+  }
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  uint8_t *codes = static_cast<uint8_t *>(workspace);
+  float *norms = reinterpret_cast<float *>(static_cast<unsigned char *>(workspace) +
+                                           align_up(static_cast<size_t>(out_features) * in_features, 256));
+  const float *use_norms = row_norms_in;
+  if (row_norms_in == nullptr) {
+    if (int rc = launch_weight_row_norms(weight, dtype, out_features, in_features, norms,
+                                         row_norms_bf16_out, s)) {
+      return rc;
+    }
+    use_norms = norms;
+  } else if (int rc = launch_norms_to_bf16(row_norms_in, out_features, row_norms_bf16_out, s)) {
+    return rc;
+  }
+  if (int rc = launch_rotate_quantize(weight, dtype, out_features, in_features, perm, signs, block,
+                                      boundaries, centroids, bits, eps, nullptr, codes, nullptr,
+                                      nullptr, nullptr, 0, nullptr, nullptr, 0, s, use_norms)) {
+    return rc;
+  }
+  return launch_pack(codes, bits, out_features * in_features, packed_out, s);
 }
 
 // Status word of the tcgen05 kernel's bounded waits (0 = every wait completed).  Reading

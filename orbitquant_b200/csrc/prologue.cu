@@ -59,6 +59,10 @@ struct PrologueParams {
   float *table_scale_out;
   int *zero_words;   // cleared by CTA 0 (slice counters of the kernel that follows)
   int zero_count;
+  // Weight mode (offline quantise-and-pack, reference layers.py:102-121): the row norm is
+  // GIVEN, nothing is pre-scaled, and the direction is (fwht * 1/sqrt(block)) / max(norm, eps)
+  // -- a true division, after the transform, as the reference's torch expression has it.
+  const float *given_norms;
 };
 
 // Number of boundaries strictly below `v` (sorted ascending, count = 2^bits - 1), as a
@@ -95,7 +99,10 @@ template <int DTYPE>
 __device__ __forceinline__ void emit(const PrologueParams &p, void *stage_row, uint8_t *codes_row,
                                      const float *s_bnd, const float *s_cent, int i, float v,
                                      float norm, float opscale) {
-  const float direction = __fmul_rn(v, p.inv_sqrt_block);
+  float direction = __fmul_rn(v, p.inv_sqrt_block);
+  if (p.given_norms != nullptr) {
+    direction = __fdiv_rn(direction, norm);
+  }
   const int idx = bucketize(direction, s_bnd, p.bits);
   const float q = __fmul_rn(s_cent[idx], norm);
   if (p.f16_operand) {
@@ -205,9 +212,13 @@ rotate_quantize_kernel(const PrologueParams p) {
   // A kernel launched with programmatic stream serialization may start its own set-up now;
   // it still waits (griddepcontrol.wait) for this grid to finish before it reads our output.
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
-  if (blockIdx.x == 0 && p.table_scale_out != nullptr) {
+  // The last CTA of the grid does nothing but the table-scale search and the counter clearing,
+  // so that with few rows (decode) they are not on any token's critical path.
+  const int workers = static_cast<int>(gridDim.x) - (p.table_scale_out != nullptr ? 1 : 0);
+  if (static_cast<int>(blockIdx.x) == workers) {
     clear_words(p.zero_words, p.zero_count);
-    search_table_scale(p.w_centroids, p.w_bits, p.table_scale_out, s_bnd);  // tables not filled yet
+    search_table_scale(p.w_centroids, p.w_bits, p.table_scale_out, s_bnd);
+    return;
   }
   const int levels = 1 << p.bits;
   for (int i = threadIdx.x; i < levels; i += kThreads) {
@@ -227,7 +238,7 @@ rotate_quantize_kernel(const PrologueParams p) {
   const bool vec_ok = (dim % kVec) == 0;
 
   for (int64_t row_base = static_cast<int64_t>(blockIdx.x) * R; row_base < p.rows;
-       row_base += static_cast<int64_t>(gridDim.x) * R) {
+       row_base += static_cast<int64_t>(workers) * R) {
     const int nrows = static_cast<int>(min(static_cast<int64_t>(R), p.rows - row_base));
     __syncthreads();  // previous iteration's stores are done with the staging buffer
 
@@ -282,9 +293,14 @@ rotate_quantize_kernel(const PrologueParams p) {
           const float v = static_cast<float>(xr[i]);
           acc = __fadd_rn(acc, __fmul_rn(v, v));
         }
-        const float norm = __fsqrt_rn(acc);
+        float norm = __fsqrt_rn(acc);
+        float inv = __fdiv_rn(1.0f, __fadd_rn(norm, p.eps));
+        if (p.given_norms != nullptr) {
+          norm = fmaxf(p.given_norms[row_base + r], p.eps);  // clamp_min(eps); the divisor
+          inv = 1.0f;                                        // x * 1 is exact: no pre-scaling
+        }
         s_norm[r] = norm;
-        s_inv[r] = __fdiv_rn(1.0f, __fadd_rn(norm, p.eps));
+        s_inv[r] = inv;
         if (p.norms != nullptr) {
           p.norms[row_base + r] = norm;
         }
@@ -454,7 +470,8 @@ int launch_rotate_quantize(const void *x, int x_dtype, int64_t rows, int64_t dim
                            const float *boundaries, const float *centroids, int bits, float eps,
                            void *x_q, uint8_t *codes, float *norms, float *f16_row_scale,
                            const float *w_centroids, int w_bits, float *table_scale_out,
-                           int *zero_words, int zero_count, cudaStream_t stream) {
+                           int *zero_words, int zero_count, cudaStream_t stream,
+                           const float *given_norms) {
   OQ_CHECK_ARG(table_scale_out == nullptr || (w_centroids != nullptr && w_bits >= 1 && w_bits <= 8),
                "the table scale search needs the weight codebook");
   OQ_CHECK_ARG(f16_row_scale == nullptr || (x_dtype != OQ_DTYPE_F32 && x_q != nullptr),
@@ -538,9 +555,11 @@ int launch_rotate_quantize(const void *x, int x_dtype, int64_t rows, int64_t dim
   p.table_scale_out = table_scale_out;
   p.zero_words = zero_words;
   p.zero_count = zero_words != nullptr ? zero_count : 0;
+  p.given_norms = given_norms;
 
   const int64_t ctas_needed = (rows + rows_per_cta - 1) / rows_per_cta;
-  const int grid = static_cast<int>(std::min<int64_t>(ctas_needed, static_cast<int64_t>(sm_count) * 8));
+  const int grid = static_cast<int>(std::min<int64_t>(ctas_needed, static_cast<int64_t>(sm_count) * 8)) +
+                   (table_scale_out != nullptr ? 1 : 0);  // + the search CTA
   void (*kernel)(PrologueParams) = nullptr;
   switch (x_dtype) {
     case OQ_DTYPE_F32: kernel = rotate_quantize_kernel<OQ_DTYPE_F32>; break;
@@ -555,6 +574,68 @@ int launch_rotate_quantize(const void *x, int x_dtype, int64_t rows, int64_t dim
                                        static_cast<int>(smem)));
   }
   kernel<<<grid, kThreads, smem, stream>>>(p);
+  OQ_CHECK_CUDA(cudaGetLastError());
+  count_launch();
+  return OQ_OK;
+}
+
+namespace {
+
+// L2 norm of every weight row, accumulated in double (one warp per row, fixed order) and
+// rounded once to fp32: at least as accurate as any fp32 reduction order, and deterministic.
+template <int DTYPE>
+__global__ void __launch_bounds__(256) weight_row_norms_kernel(const void *w, int64_t rows, int64_t dim,
+                                                               float *norms_f32,
+                                                               __nv_bfloat16 *norms_bf16) {
+  const int lane = threadIdx.x & 31;
+  const int64_t row = static_cast<int64_t>(blockIdx.x) * 8 + (threadIdx.x >> 5);
+  if (row >= rows) {
+    return;
+  }
+  double acc = 0.0;
+  for (int64_t i = lane; i < dim; i += 32) {
+    const double v = static_cast<double>(Scalar<DTYPE>::load(w, row * dim + i));
+    acc = fma(v, v, acc);
+  }
+#pragma unroll
+  for (int m = 16; m >= 1; m >>= 1) {
+    acc += __shfl_xor_sync(0xffffffffu, acc, m);
+  }
+  if (lane == 0) {
+    const float norm = static_cast<float>(sqrt(acc));
+    norms_f32[row] = norm;
+    if (norms_bf16 != nullptr) {
+      norms_bf16[row] = __float2bfloat16_rn(norm);
+    }
+  }
+}
+
+__global__ void norms_to_bf16_kernel(const float *norms, int64_t rows, __nv_bfloat16 *out) {
+  const int64_t i = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x;
+  if (i < rows) {
+    out[i] = __float2bfloat16_rn(norms[i]);
+  }
+}
+
+}  // namespace
+
+int launch_weight_row_norms(const void *w, int dtype, int64_t rows, int64_t dim, float *norms_f32,
+                            void *norms_bf16, cudaStream_t stream) {
+  const unsigned grid = static_cast<unsigned>((rows + 7) / 8);
+  __nv_bfloat16 *bf = static_cast<__nv_bfloat16 *>(norms_bf16);
+  switch (dtype) {
+    case OQ_DTYPE_F32: weight_row_norms_kernel<OQ_DTYPE_F32><<<grid, 256, 0, stream>>>(w, rows, dim, norms_f32, bf); break;
+    case OQ_DTYPE_F16: weight_row_norms_kernel<OQ_DTYPE_F16><<<grid, 256, 0, stream>>>(w, rows, dim, norms_f32, bf); break;
+    default: weight_row_norms_kernel<OQ_DTYPE_BF16><<<grid, 256, 0, stream>>>(w, rows, dim, norms_f32, bf); break;
+  }
+  OQ_CHECK_CUDA(cudaGetLastError());
+  count_launch();
+  return OQ_OK;
+}
+
+int launch_norms_to_bf16(const float *norms, int64_t rows, void *out, cudaStream_t stream) {
+  norms_to_bf16_kernel<<<static_cast<unsigned>((rows + 255) / 256), 256, 0, stream>>>(
+      norms, rows, static_cast<__nv_bfloat16 *>(out));
   OQ_CHECK_CUDA(cudaGetLastError());
   count_launch();
   return OQ_OK;

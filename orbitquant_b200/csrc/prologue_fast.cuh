@@ -145,9 +145,13 @@ rotate_quantize_fast_kernel(const PrologueParams p) {
   uint16_t *s_outtab = reinterpret_cast<uint16_t *>(s_opscale + 8);                 // [R][kLevels]
 
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");  // see rotate_quantize_kernel
-  if (blockIdx.x == 0 && p.table_scale_out != nullptr) {
+  // The last CTA of the grid does nothing but the table-scale search and the counter clearing,
+  // so that with few rows (decode) they are not on any token's critical path.
+  const int workers = static_cast<int>(gridDim.x) - (p.table_scale_out != nullptr ? 1 : 0);
+  if (static_cast<int>(blockIdx.x) == workers) {
     clear_words(p.zero_words, p.zero_count);
-    search_table_scale(p.w_centroids, p.w_bits, p.table_scale_out, rot);  // token buffers still free
+    search_table_scale(p.w_centroids, p.w_bits, p.table_scale_out, rot);
+    return;
   }
   for (int i = threadIdx.x; i < kLevels; i += kFastThreads) {
     s_cent[i] = p.centroids[i];
@@ -162,7 +166,7 @@ rotate_quantize_fast_kernel(const PrologueParams p) {
   const float isb = p.inv_sqrt_block;
 
   for (int64_t row_base = static_cast<int64_t>(blockIdx.x) * R; row_base < p.rows;
-       row_base += static_cast<int64_t>(gridDim.x) * R) {
+       row_base += static_cast<int64_t>(workers) * R) {
     const int nrows = static_cast<int>(min(static_cast<int64_t>(R), p.rows - row_base));
     __syncthreads();
 

@@ -113,6 +113,21 @@ def quantize_weight(weight: torch.Tensor, *, rotation: RPBHRotation, codebook, b
     return packed.to(device), norms_out.to(device)
 
 
+def quantize_weight_gpu(weight: torch.Tensor, *, rotation: RPBHRotation, codebook, bits: int,
+                        eps: float, row_norms: torch.Tensor | None = None
+                        ) -> tuple[torch.Tensor, torch.Tensor]:
+    """``quantize_weight`` on the GPU (``oq_quantize_weight``): same arithmetic per element
+    (rotate, ``* 1/sqrt(block)``, divide by ``max(norm, eps)``, bucketize, pack).  Given the
+    same fp32 ``row_norms`` the packed stream is bit-identical to the CPU path; without them
+    the norms are computed on the device with double accumulation, which can differ from
+    torch's CPU reduction in the last bit of a norm (and then flip an index that sits within
+    one ulp of a boundary)."""
+    return native.quantize_weight_packed(
+        weight, permutation=rotation.permutation, signs=rotation.signs,
+        block_size=rotation.block_size, boundaries=codebook.boundaries, centroids=codebook.centroids,
+        bits=bits, eps=eps, row_norms=row_norms)
+
+
 def _linear_spec(layer: nn.Module) -> tuple[int, int]:
     weight = getattr(layer, "weight", None)
     if not isinstance(layer, nn.Linear) or not isinstance(weight, torch.Tensor) or weight.ndim != 2:
@@ -193,13 +208,14 @@ class OrbitQuantLinear(nn.Module):
     # ---- construction -------------------------------------------------------------------
 
     @classmethod
-    def from_linear(cls, layer: nn.Module, *, config: OrbitQuantConfig,
-                    module_name: str) -> "OrbitQuantLinear":
+    def from_linear(cls, layer: nn.Module, *, config: OrbitQuantConfig, module_name: str,
+                    quantization_device: torch.device | None = None) -> "OrbitQuantLinear":
         in_features, out_features = _linear_spec(layer)
         bias = None if layer.bias is None else layer.bias.detach()
         return cls.from_weight(layer.weight.detach(), bias=bias, in_features=in_features,
                                out_features=out_features, source_weight_layout="out_in",
-                               config=config, module_name=module_name)
+                               config=config, module_name=module_name,
+                               quantization_device=quantization_device)
 
     @classmethod
     def from_weight(cls, weight: torch.Tensor, *, bias: torch.Tensor | None, in_features: int,
@@ -212,9 +228,17 @@ class OrbitQuantLinear(nn.Module):
         rotation = get_rpbh_rotation(dim=in_features, seed=config.rotation_seed,
                                      block_size=config.block_size)
         codebook = get_codebook(in_features, config.weight_bits, config.codebook_version)
-        packed, row_norms = quantize_weight(
-            weight, rotation=rotation, codebook=codebook, bits=config.weight_bits,
-            eps=config.activation_eps, row_tile_size=config.weight_row_tile_size)
+        on_gpu = (quantization_device is not None and torch.device(quantization_device).type == "cuda")
+        if on_gpu:
+            # the library's quantise-and-pack kernels (norm, RPBH, bucketize, bit stream)
+            packed, row_norms = quantize_weight_gpu(
+                weight.detach().to(quantization_device), rotation=rotation, codebook=codebook,
+                bits=config.weight_bits, eps=config.activation_eps)
+            packed, row_norms = packed.to(weight.device), row_norms.to(weight.device)
+        else:
+            packed, row_norms = quantize_weight(
+                weight, rotation=rotation, codebook=codebook, bits=config.weight_bits,
+                eps=config.activation_eps, row_tile_size=config.weight_row_tile_size)
         return cls(in_features=in_features, out_features=out_features, config=config,
                    module_name=module_name, source_weight_layout=source_weight_layout, bias=bias,
                    packed_weight_indices=packed, row_norms=row_norms, debug_weight=None)

@@ -51,6 +51,9 @@ _SIGNATURES = {
     "oq_linear_forward_scatter": (_int, [_vp, _int, _i64, _i64, _vp, _int, _i64, _i64, _i64, _vp, _i64,
                                          _int, _vp, _vp, _vp, _int, _vp, _vp, _i64, _vp, _vp, _int,
                                          _f32, _vp, _sz, _vp]),
+    "oq_quantize_weight": (_int, [_vp, _int, _i64, _i64, _vp, _vp, _i64, _vp, _vp, _int, _f32, _vp, _vp,
+                                  _vp, _vp, _sz, _vp]),
+    "oq_quantize_weight_workspace_bytes": (_sz, [_i64, _i64]),
     "oq_static_scratch_bytes": (_sz, []),
     "oq_linear_workspace_bytes": (_sz, [_i64, _i64, _i64, _int, _int, _int, _int]),
     "oq_gemm_device_status": (_int, [ctypes.POINTER(ctypes.c_int)]),
@@ -348,3 +351,34 @@ def linear_forward_scatter(x, packed, row_norms, bias, *, out_ptrs, out_ld, out_
             _ptr(weight_centroids), _ptr(bias), bias_code, _ptr(permutation), _ptr(signs),
             int(block_size), _ptr(act_boundaries), _ptr(act_centroids), act_bits, float(eps),
             _ptr(ws), ws_bytes, _stream(device)))
+
+
+def quantize_weight_packed(weight, *, permutation, signs, block_size, boundaries, centroids, bits,
+                           eps, row_norms=None):
+    """Offline weight quantisation on the GPU: ``weight [N, K]`` (CUDA) -> (packed uint8 stream,
+    bf16 row norms).  ``row_norms`` (f32 ``[N]``) pins the norms, e.g. to the ones a CPU
+    reference computed; otherwise they are computed on the device."""
+    _require_cuda("weight", weight)
+    if weight.ndim != 2:
+        raise ValueError("weight must be a matrix")
+    if weight.dtype not in DTYPE_CODES:
+        raise ValueError("weight must be float32, float16, or bfloat16")
+    device = weight.device
+    w = weight.contiguous()
+    n, k = w.shape
+    perm = permutation.to(device=device, dtype=torch.int32).contiguous()
+    sg = signs.to(device=device, dtype=torch.int8).contiguous()
+    bnd = boundaries.to(device=device, dtype=torch.float32).contiguous()
+    cent = centroids.to(device=device, dtype=torch.float32).contiguous()
+    norms_in = None if row_norms is None else row_norms.to(device=device, dtype=torch.float32).contiguous()
+    packed = torch.empty((n * k * bits + 7) // 8, dtype=torch.uint8, device=device)
+    norms_out = torch.empty(n, dtype=torch.bfloat16, device=device)
+    lib = load()
+    ws_bytes = lib.oq_quantize_weight_workspace_bytes(n, k)
+    ws = torch.empty(max(ws_bytes, 16), dtype=torch.uint8, device=device)
+    with torch.cuda.device(device):
+        _check(lib.oq_quantize_weight(
+            _ptr(w), DTYPE_CODES[w.dtype], n, k, _ptr(perm), _ptr(sg), int(block_size), _ptr(bnd),
+            _ptr(cent), int(bits), float(eps), _ptr(norms_in), _ptr(norms_out), _ptr(packed),
+            _ptr(ws), ws_bytes, _stream(device)))
+    return packed, norms_out
