@@ -63,6 +63,10 @@ struct PrologueParams {
   // GIVEN, nothing is pre-scaled, and the direction is (fwht * 1/sqrt(block)) / max(norm, eps)
   // -- a true division, after the transform, as the reference's torch expression has it.
   const float *given_norms;
+  // Few rows (decode): a row is split over `slices` CTAs along whole rotation blocks.  Every
+  // CTA still loads the row and computes its norm (both are needed everywhere and cheap), but
+  // transforms, quantises and stores only its own blocks.  1 = no split.  Fast kernel only.
+  int slices;
 };
 
 // Number of boundaries strictly below `v` (sorted ascending, count = 2^bits - 1), as a
@@ -556,8 +560,22 @@ int launch_rotate_quantize(const void *x, int x_dtype, int64_t rows, int64_t dim
   p.zero_words = zero_words;
   p.zero_count = zero_words != nullptr ? zero_count : 0;
   p.given_norms = given_norms;
+  p.slices = 1;
 
-  const int64_t ctas_needed = (rows + rows_per_cta - 1) / rows_per_cta;
+  if (fast != nullptr && rows * 2 <= sm_count) {
+    // largest divisor of the number of rotation blocks that keeps the grid within the machine
+    const int blocks_per_row = static_cast<int>(dim / block);
+    for (int cand = blocks_per_row; cand >= 2; --cand) {
+      if (blocks_per_row % cand == 0 && rows * cand <= 2 * sm_count) {
+        p.slices = cand;
+        break;
+      }
+    }
+    if (p.slices > 1) {
+      p.rows_per_cta = 1;
+    }
+  }
+  const int64_t ctas_needed = p.slices > 1 ? rows * p.slices : (rows + rows_per_cta - 1) / rows_per_cta;
   const int grid = static_cast<int>(std::min<int64_t>(ctas_needed, static_cast<int64_t>(sm_count) * 8)) +
                    (table_scale_out != nullptr ? 1 : 0);  // + the search CTA
   void (*kernel)(PrologueParams) = nullptr;

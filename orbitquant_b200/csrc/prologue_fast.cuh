@@ -165,8 +165,14 @@ rotate_quantize_fast_kernel(const PrologueParams p) {
   const unsigned char *bnd_bytes = reinterpret_cast<const unsigned char *>(s_bnd);
   const float isb = p.inv_sqrt_block;
 
-  for (int64_t row_base = static_cast<int64_t>(blockIdx.x) * R; row_base < p.rows;
-       row_base += static_cast<int64_t>(workers) * R) {
+  // Work items: groups of R rows, or (row, slice of whole rotation blocks) when rows are few.
+  const int slices = p.slices;
+  const int slice_chunks = chunks / slices;
+  const int64_t items_total = slices > 1 ? p.rows * slices : (p.rows + R - 1) / R;
+  for (int64_t work = blockIdx.x; work < items_total; work += workers) {
+    const int64_t row_base = slices > 1 ? work / slices : work * R;
+    const int c_lo = slices > 1 ? static_cast<int>(work % slices) * slice_chunks : 0;
+    const int c_hi = slices > 1 ? c_lo + slice_chunks : chunks;
     const int nrows = static_cast<int>(min(static_cast<int64_t>(R), p.rows - row_base));
     __syncthreads();
 
@@ -221,7 +227,9 @@ rotate_quantize_fast_kernel(const PrologueParams p) {
             mult = ldexpf(1.0f, 14 - e);
             back = ldexpf(1.0f, e - 14);
           }
-          p.row_scale[row_base + r] = back;
+          if (c_lo == 0) {
+            p.row_scale[row_base + r] = back;
+          }
         }
         s_opscale[r] = mult;
       }
@@ -244,10 +252,11 @@ rotate_quantize_fast_kernel(const PrologueParams p) {
     __syncthreads();
 
     // 3. gather + complete 256-point transform per (token, chunk)
-    const int items = nrows * chunks;
+    const int my_chunks = c_hi - c_lo;
+    const int items = nrows * my_chunks;
     for (int item = warp; item < items; item += kFastWarps) {
-      const int r = item / chunks;
-      const int c = item - r * chunks;
+      const int r = item / my_chunks;
+      const int c = c_lo + (item - r * my_chunks);
       const int i0 = (c << 8) + lane * 8;
       const uint16_t *xr = xin + r * dim;
       const float inv = s_inv[r];
@@ -293,22 +302,27 @@ rotate_quantize_fast_kernel(const PrologueParams p) {
     __syncthreads();
 
     // 4. widths >= 256
+    // A slice is a run of whole blocks, so the strided passes see it as a shorter row (with
+    // one row per CTA the row pitch does not matter).
+    const int span = slices > 1 ? my_chunks << 8 : dim;
+    const int first = c_lo << 8;
     if (wide) {
       int stride = 256;
       while (p.block / stride > 16) {
-        fast_strided_any<BITS, false>(rot, stage, bnd_bytes, s_outtab, dim, nrows, stride, 16, isb);
+        fast_strided_any<BITS, false>(rot + first, stage + first, bnd_bytes, s_outtab, span, nrows, stride, 16, isb);
         stride *= 16;
         __syncthreads();
       }
-      fast_strided_any<BITS, true>(rot, stage, bnd_bytes, s_outtab, dim, nrows, stride, p.block / stride, isb);
+      fast_strided_any<BITS, true>(rot + first, stage + first, bnd_bytes, s_outtab, span, nrows, stride,
+                                   p.block / stride, isb);
       __syncthreads();
     }
 
     // 5. store
     {
-      const uint4 *s4 = reinterpret_cast<const uint4 *>(stage);
-      uint4 *d4 = reinterpret_cast<uint4 *>(static_cast<uint16_t *>(p.xq) + row_base * dim);
-      const int vecs = nrows * dim / 8;
+      const uint4 *s4 = reinterpret_cast<const uint4 *>(stage + first);
+      uint4 *d4 = reinterpret_cast<uint4 *>(static_cast<uint16_t *>(p.xq) + row_base * dim + first);
+      const int vecs = slices > 1 ? span / 8 : nrows * dim / 8;
       for (int i = threadIdx.x; i < vecs; i += kFastThreads) {
         d4[i] = s4[i];
       }
