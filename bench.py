@@ -478,10 +478,22 @@ def main():
     # or, with --gather nccl, by an all-gather collective after the kernel.
     fused_gather = distributed and args.gather == "epilogue" and rows > 128
     peers = {}
+    gather_note = None
     if fused_gather:
         from orbitquant_b200.sharding import PeerOutput
-        for i, (_name, _k, n, _g, _m) in enumerate(layers):
-            peers[i] = PeerOutput(rows, n, device)
+        ok = 1
+        try:
+            for i, (_name, _k, n, _g, _m) in enumerate(layers):
+                peers[i] = PeerOutput(rows, n, device)
+        except Exception as exc:  # symmetric memory unavailable on this box: all ranks fall back together
+            ok = 0
+            gather_note = f"symmetric memory unavailable ({type(exc).__name__}); NCCL all-gather used"
+        flag = torch.tensor([ok], device=device)
+        dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+        if int(flag.item()) == 0:
+            fused_gather = False
+            peers = {}
+            gather_note = gather_note or "a peer could not map symmetric memory; NCCL all-gather used"
 
     def sharded_forward(i, x, want_full):
         _name, _k, n, _g, module = layers[i]
@@ -651,7 +663,7 @@ def main():
                 "l2": "per-step working set (inputs+weights+outputs) exceeds the 126 MB L2; no flush",
                 "parallelism": f"n_shard{world}" if distributed else "single",
                 "gather": ("gemm epilogue stores into every rank's buffer (peer memory), one barrier"
-                           if fused_gather else "nccl all_gather_into_tensor") if distributed else None,
+                           if fused_gather else (gather_note or "nccl all_gather_into_tensor")) if distributed else None,
                 "weight_mode": "centroid (f16 centroid operand, row norm in the epilogue)",
             },
             "roofline": roofline,
