@@ -206,6 +206,22 @@ int oq_quantize_weight(const void *weight, int dtype, int64_t out_features, int6
 
 size_t oq_quantize_weight_workspace_bytes(int64_t out_features, int64_t in_features);
 
+/* ---- RTN-INT4 linear (AdaLN modulation layers) ------------------------------------------- */
+
+/* out[m, n] = bf16( sum_k x[m, k] * bf16((code[n, k] - 8) * scale[n, k / 64]) + bias[n] ),
+ * fp32 accumulation: the reference's RTNInt4Linear forward (src/orbitquant/adaln.py:294-430)
+ * in the arithmetic of its CPU kernel (orbitquant_packed_matmul_cpu/packed_adaln_cpu.cpp:54-100).
+ * x, out: bf16 row-major; packed: 4-bit codes, two per byte (low nibble = even k), every row
+ * padded to ceil(in_features / 64) * 64 values; scales_bf16: [out_features, ceil(K / 64)];
+ * group_size must be 64; in_features a multiple of 8.  Runs on the few-token tensor-core
+ * kernel (bf16 x bf16), 128 rows per launch. */
+int oq_rtn_int4_linear_forward(void *out, const void *x_bf16, int64_t rows, int64_t in_features,
+                               int64_t out_features, const uint8_t *packed, int64_t packed_bytes,
+                               const void *scales_bf16, int group_size, const void *bias,
+                               int bias_dtype, void *workspace, size_t workspace_bytes, void *stream);
+
+size_t oq_rtn_int4_workspace_bytes(int64_t rows, int64_t in_features, int64_t out_features);
+
 /* ---- column-sharded layers: forward with the all-gather in the epilogue ----------------- */
 
 /* oq_linear_forward whose result tile is stored into EVERY one of `n_outs` (1..8) row-major

@@ -139,3 +139,30 @@ def linear_forward(x, packed, row_norms, bias, *, perm, signs, block, act_bounda
                                      eps=eps, norm_order=norm_order)
     return matmul_packed(x_q, packed, row_norms, w_centroids, bits=w_bits,
                          out_features=out_features, bias=bias, mode=mode)
+
+
+def rtn_int4_matmul(x, packed, scales, *, out_features, in_features, group_size=64, bias=None):
+    """RTN-INT4 group linear as the reference's scalar CPU kernel defines it
+    (``orbitquant_packed_matmul_cpu/packed_adaln_cpu.cpp:54-100``): weight value
+    ``bf16((code - 8) * scale)``, fp32 products accumulated over k in ascending order in fp32,
+    ``+ bias``, rounded to bf16.  numpy restatement (test infrastructure; small sizes)."""
+    import numpy as np
+
+    groups = (in_features + group_size - 1) // group_size
+    padded = groups * group_size
+    raw = packed.cpu().numpy().astype(np.uint8)
+    codes = np.empty(raw.size * 2, dtype=np.int32)
+    codes[0::2] = raw & 15
+    codes[1::2] = raw >> 4
+    codes = codes[: out_features * padded].reshape(out_features, padded) - 8
+    scale = scales.cpu().to(torch.float32).numpy().reshape(out_features, groups)
+    dense = (codes.astype(np.float32).reshape(out_features, groups, group_size) * scale[..., None]).astype(np.float32)
+    weight = torch.from_numpy(dense.reshape(out_features, padded)[:, :in_features].copy()).to(torch.bfloat16).to(torch.float32).numpy()
+    x2 = x.to(torch.bfloat16).to(torch.float32).reshape(-1, in_features).cpu().numpy()
+    acc = np.zeros((x2.shape[0], out_features), dtype=np.float32)
+    for k in range(in_features):   # ascending k, one fp32 rounding per product and per add
+        acc += (x2[:, k:k + 1] * weight[None, :, k]).astype(np.float32)
+    if bias is not None:
+        acc += bias.cpu().to(torch.float32).numpy()[None, :]
+    out = torch.from_numpy(acc).to(torch.bfloat16)
+    return out.reshape(*x.shape[:-1], out_features)

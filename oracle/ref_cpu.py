@@ -117,3 +117,21 @@ def linear_forward(x, packed, row_norms, bias, *, permutation, signs, act_centro
     return matmul_packed_weight(
         x_q, packed, row_norms, w_centroids, bits=w_bits, out_features=out_features,
         in_features=in_features, bias=bias)
+
+
+def matmul_packed_adaln_int4(x, packed, scales, *, out_features, in_features, group_size=64, bias=None):
+    """The reference's CPU RTN-INT4 kernel (``packed_adaln_cpu.cpp:807-878``): bf16 x, fp32
+    scales ``[N, groups]``, fp32 bias -> bf16."""
+    x2 = x.to(torch.bfloat16).contiguous().reshape(-1, in_features)
+    out = torch.empty((x2.shape[0], out_features), dtype=torch.bfloat16)
+    if bias is None:
+        bias_values = torch.empty((1,), dtype=torch.float32)
+        has_bias = False
+    else:
+        bias_values = bias.to(device="cpu", dtype=torch.float32).contiguous()
+        has_bias = True
+    _ops().matmul_packed_adaln_int4_cpu(
+        out, x2, packed.to(device="cpu", dtype=torch.uint8).contiguous(),
+        scales.to(device="cpu", dtype=torch.float32).contiguous(), bias_values, has_bias,
+        int(out_features), int(in_features), int(group_size))
+    return out.reshape(*x.shape[:-1], out_features)

@@ -5,6 +5,7 @@ Public surface (same names as the reference package for this path):
 ``pack_lowbit`` / ``unpack_lowbit``, ``quantize_activations`` and the registered custom op
 ``torch.ops.orbitquant.packed_linear_forward``.
 """
+from .adaln import RTNInt4Linear, quantize_adaln_weight
 from .artifacts import load_orbitquant_artifact
 from .codebooks import LloydMaxCodebook, get_codebook
 from .config import OrbitQuantConfig
@@ -15,6 +16,8 @@ from .rotations import RPBHRotation, fwht, get_rpbh_rotation
 
 __all__ = [
     "load_orbitquant_artifact",
+    "RTNInt4Linear",
+    "quantize_adaln_weight",
     "LloydMaxCodebook", "OrbitQuantConfig", "OrbitQuantLinear", "RPBHRotation", "fwht",
     "get_codebook", "get_rpbh_rotation", "pack_lowbit", "packed_length", "quantize_activations",
     "quantize_weight", "unpack_lowbit",

@@ -10,7 +10,8 @@ for the files the quantized-linear forward needs, as its writer lays them out
   the config), ``adaln_modules``, ``checksums`` (sha256 per file);
 * ``model.safetensors`` -- the model's state dict; a quantized leaf contributes exactly
   ``<name>.packed_weight_indices`` (flat uint8 bit stream), ``<name>.row_norms`` (bf16) and,
-  when present, ``<name>.bias``;
+  when present, ``<name>.bias``; an RTN-INT4 (AdaLN) leaf ``<name>.packed_weight``,
+  ``<name>.scales`` (bf16 ``[out_features, groups]``) and ``<name>.bias``;
 * ``orbitquant_rotations.safetensors`` / ``orbitquant_codebooks.safetensors`` -- the RPBH
   permutation / signs per ``(dim, seed, block)`` and the Lloyd-Max tables per ``(dim, bits)``.
 
@@ -28,6 +29,7 @@ from pathlib import Path
 
 import torch
 
+from .adaln import RTNInt4Linear
 from .config import OrbitQuantConfig
 from .layers import OrbitQuantLinear
 
@@ -97,8 +99,8 @@ def load_orbitquant_artifact(model: torch.nn.Module, artifact_dir, *, strict: bo
     with a CUDA device safetensors reads straight into device memory and the modules are
     ready to run.  ``validate_checksums`` checks the sha256 of every file this loader reads
     against the manifest (the reference additionally insists on its model card and prompt
-    files, which a runtime does not need).  RTN-INT4 AdaLN modules are outside this package:
-    an artifact that lists any is refused."""
+    files, which a runtime does not need).  The manifest's ``adaln_modules`` become
+    ``RTNInt4Linear`` modules."""
     from safetensors.torch import load_file
 
     artifact = Path(artifact_dir)
@@ -118,10 +120,6 @@ def load_orbitquant_artifact(model: torch.nn.Module, artifact_dir, *, strict: bo
                 raise ValueError(f"manifest holds no checksum for {name}")
             if sha256_file(artifact / name) != sums[name]:
                 raise ValueError(f"checksum mismatch for {name}")
-    if manifest.get("adaln_modules"):
-        raise NotImplementedError("the artifact contains RTN-INT4 AdaLN modules, which this package "
-                                  "does not implement: " + ", ".join(manifest["adaln_modules"]))
-
     module_bits = manifest.get("module_bits", {})
     for name in manifest.get("quantized_modules", []):
         module = model.get_submodule(name)
@@ -132,6 +130,14 @@ def load_orbitquant_artifact(model: torch.nn.Module, artifact_dir, *, strict: bo
         if bits is not None and bits != config.weight_bits:
             module_config = dataclasses.replace(config, weight_bits=int(bits))
         replacement = OrbitQuantLinear.empty_from_linear(module, config=module_config, module_name=name)
+        parent, child = _parent_and_child(model, name)
+        _set_child(parent, child, replacement)
+
+    for name in manifest.get("adaln_modules", []):
+        module = model.get_submodule(name)
+        if not isinstance(module, torch.nn.Linear):
+            raise TypeError(f"expected Linear at {name}, got {type(module).__name__}")
+        replacement = RTNInt4Linear.empty_from_linear(module, config=config, module_name=name)
         parent, child = _parent_and_child(model, name)
         _set_child(parent, child, replacement)
 

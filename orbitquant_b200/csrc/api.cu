@@ -76,6 +76,11 @@ int launch_tcgen05_gemm_scatter(void *const *outs, int n_outs, int64_t out_ld, i
                                 const uint8_t *packed, int bits, const void *row_norms_bf16,
                                 const float *centroids, const void *bias, int bias_dtype,
                                 cudaStream_t stream);
+size_t tcgen05_rtn_workspace_bytes(int64_t rows, int64_t in_features, int64_t out_features);
+int launch_tcgen05_rtn_int4(void *out, const void *x_bf16, int64_t rows, int64_t in_features,
+                            int64_t out_features, const uint8_t *packed, const void *scales_bf16,
+                            const void *bias, int bias_dtype, void *workspace,
+                            size_t workspace_bytes, cudaStream_t stream);
 int read_gemm_status(int *status);
 int clear_gemm_status();
 
@@ -586,6 +591,43 @@ int oq_quantize_weight(const void *weight, int dtype, int64_t out_features, int6
     return rc;
   }
   return launch_pack(codes, bits, out_features * in_features, packed_out, s);
+}
+
+size_t oq_rtn_int4_workspace_bytes(int64_t rows, int64_t in_features, int64_t out_features) {
+  if (rows <= 0 || in_features <= 0 || out_features <= 0) {
+    return 0;
+  }
+  return tcgen05_rtn_workspace_bytes(rows > 128 ? 128 : rows, in_features, out_features);
+}
+
+int oq_rtn_int4_linear_forward(void *out, const void *x_bf16, int64_t rows, int64_t in_features,
+                               int64_t out_features, const uint8_t *packed, int64_t packed_bytes,
+                               const void *scales_bf16, int group_size, const void *bias,
+                               int bias_dtype, void *workspace, size_t workspace_bytes, void *stream) {
+  OQ_CHECK_ARG(rows >= 0 && in_features > 0 && out_features >= 0, "negative or empty shape");
+  OQ_CHECK_ARG(group_size == 64, "only the group size 64 is implemented");
+  OQ_CHECK_ARG(bias == nullptr || valid_dtype(bias_dtype), "bias must be float32, float16, or bfloat16");
+  const int64_t groups = (in_features + 63) / 64;
+  OQ_CHECK_ARG(packed_bytes >= out_features * groups * 32, "packed weights are too short");
+  if (rows == 0 || out_features == 0) {
+    return OQ_OK;
+  }
+  OQ_CHECK_ARG(out && x_bf16 && packed && scales_bf16, "null device pointer");
+  if (int rc = check_device()) {
+    return rc;
+  }
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  // more than 128 rows: one launch per 128-row slab (these layers see the batch, not the tokens)
+  for (int64_t first = 0; first < rows; first += 128) {
+    const int64_t slab = rows - first < 128 ? rows - first : 128;
+    if (int rc = launch_tcgen05_rtn_int4(static_cast<unsigned char *>(out) + first * out_features * 2,
+                                         static_cast<const unsigned char *>(x_bf16) + first * in_features * 2,
+                                         slab, in_features, out_features, packed, scales_bf16, bias,
+                                         bias_dtype, workspace, workspace_bytes, s)) {
+      return rc;
+    }
+  }
+  return OQ_OK;
 }
 
 // Status word of the tcgen05 kernel's bounded waits (0 = every wait completed).  Reading

@@ -1148,6 +1148,86 @@ int launch_tcgen05_skinny(void *out, const void *x, const float *row_scale, cons
   return rc;
 }
 
+// RTN-INT4 group-64 weights (AdaLN modulation layers), 1..128 rows of bf16 activations.
+size_t tcgen05_rtn_workspace_bytes(int64_t rows, int64_t in_features, int64_t out_features) {
+  const int64_t padded = (in_features + kBK - 1) / kBK * kBK;
+  return tcgen05_skinny_workspace_bytes(rows, padded, out_features);
+}
+
+int launch_tcgen05_rtn_int4(void *out, const void *x_bf16, int64_t rows, int64_t in_features,
+                            int64_t out_features, const uint8_t *packed, const void *scales_bf16,
+                            const void *bias, int bias_dtype, void *workspace,
+                            size_t workspace_bytes, cudaStream_t stream) {
+  OQ_CHECK_ARG(aligned16(x_bf16) && aligned16(packed), "x and packed weights must be 16-byte aligned");
+  OQ_CHECK_ARG(rows >= 1 && rows <= kSkMaxTokens, "1..128 rows per launch");
+  OQ_CHECK_ARG(in_features % 8 == 0, "in_features must be a multiple of 8 (16-byte activation rows)");
+  EncodeTiledFn encode = encode_tiled_fn();
+  if (encode == nullptr) {
+    return fail(OQ_ERR_CUDA, "cuTensorMapEncodeTiled is not available from this driver");
+  }
+  int device = 0;
+  int sm_count = 0;
+  OQ_CHECK_CUDA(cudaGetDevice(&device));
+  OQ_CHECK_CUDA(cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, device));
+  const int64_t groups = (in_features + kBK - 1) / kBK;  // 64-wide groups = k steps; rows are padded to them
+  const SkinnyPlan plan = skinny_plan(rows, groups * kBK, out_features, sm_count > 256 ? 256 : sm_count);
+
+  CUtensorMap map_x;
+  CUtensorMap map_p;
+  {
+    const cuuint64_t dims[2] = {static_cast<cuuint64_t>(in_features), static_cast<cuuint64_t>(rows)};
+    const cuuint64_t strides[1] = {static_cast<cuuint64_t>(in_features) * 2};
+    const cuuint32_t box[2] = {kBK, static_cast<cuuint32_t>(plan.n_pad)};
+    const cuuint32_t elem[2] = {1, 1};
+    const CUresult rc = encode(&map_x, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void *>(x_bf16),
+                               dims, strides, box, elem, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                               CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                               CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (rc != CUDA_SUCCESS) {
+      return fail(OQ_ERR_CUDA, "cuTensorMapEncodeTiled(activations) failed with code %d", (int)rc);
+    }
+  }
+  {
+    const int64_t row_bytes = groups * 32;
+    const cuuint64_t dims[2] = {static_cast<cuuint64_t>(row_bytes), static_cast<cuuint64_t>(out_features)};
+    const cuuint64_t strides[1] = {static_cast<cuuint64_t>(row_bytes)};
+    const cuuint32_t box[2] = {32, static_cast<cuuint32_t>(kSkRows)};
+    const cuuint32_t elem[2] = {1, 1};
+    const CUresult rc = encode(&map_p, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<uint8_t *>(packed),
+                               dims, strides, box, elem, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                               CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                               CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (rc != CUDA_SUCCESS) {
+      return fail(OQ_ERR_CUDA, "cuTensorMapEncodeTiled(packed weights) failed with code %d", (int)rc);
+    }
+  }
+  SkinnyParams p{};
+  p.out = out;
+  p.packed = packed;
+  p.rtn_scales = static_cast<const __nv_bfloat16 *>(scales_bf16);
+  p.bias = bias;
+  p.bias_dtype = bias == nullptr ? -1 : bias_dtype;
+  p.rows = static_cast<int>(rows);
+  p.out_features = out_features;
+  p.k_iters = static_cast<int>(groups);
+  p.n_pad = plan.n_pad;
+  p.splits = plan.splits;
+  p.chunk_iters = plan.chunk_iters;
+  p.n_tiles = plan.n_tiles;
+  if (plan.splits > 1) {
+    const size_t need = skinny_partial_bytes(plan, out_features);
+    if (workspace == nullptr || workspace_bytes < need) {
+      return fail(OQ_ERR_WORKSPACE, "workspace of %zu bytes given, %zu needed", workspace_bytes, need);
+    }
+    OQ_CHECK_ARG(aligned16(workspace), "workspace must be 16-byte aligned");
+    p.counters = static_cast<int *>(workspace);
+    p.partial = reinterpret_cast<float *>(static_cast<unsigned char *>(workspace) + skinny_counter_bytes(plan));
+    // no kernel of this library runs before this one: clear the slice counters with a memset node
+    OQ_CHECK_CUDA(cudaMemsetAsync(workspace, 0, skinny_counter_bytes(plan), stream));
+  }
+  return launch_skinny_bits<4, true>(map_x, map_p, p, sm_count, stream);
+}
+
 int read_gemm_status(int *status) {
   OQ_CHECK_CUDA(cudaMemcpyFromSymbol(status, g_gemm_status, sizeof(int)));
   return OQ_OK;

@@ -88,6 +88,9 @@ struct SkinnyParams {
   int copy_stage_bytes;
   int slots;               // ring of expanded weight tiles
   int debug_skip;          // profiling only: 1 = expanders skip the decode
+  // RTN-INT4 group-64 weights (the AdaLN modulation layers): value = bf16((code - 8) * scale),
+  // one bf16 scale per weight row and 64-wide k step; both MMA operands are then bf16.
+  const __nv_bfloat16 *rtn_scales;  // [out_features][k_iters]
 };
 
 __device__ __forceinline__ void tmem_ld_32x32b_x16(uint32_t taddr, uint32_t (&v)[16]) {
@@ -108,8 +111,10 @@ __device__ __forceinline__ void tma_prefetch_l2_2d(const CUtensorMap *map, int x
 }
 
 // Instruction descriptor with a run-time N (tokens): f32 accumulator, f16 x f16, M = 128.
-__device__ __forceinline__ uint32_t instr_desc_tokens(int n) {
-  return (1u << 4) | (static_cast<uint32_t>(n >> 3) << 17) | (static_cast<uint32_t>(128 >> 4) << 24);
+__device__ __forceinline__ uint32_t instr_desc_tokens(int n, bool bf16_operands) {
+  const uint32_t format = bf16_operands ? 1u : 0u;  // A and B always share one format
+  return (1u << 4) | (format << 7) | (format << 10) | (static_cast<uint32_t>(n >> 3) << 17) |
+         (static_cast<uint32_t>(128 >> 4) << 24);
 }
 
 // Position in a ring of `size` entries and the parity of its current pass.
@@ -143,7 +148,7 @@ __device__ __forceinline__ SkinnyUnit skinny_unit(const SkinnyParams &p, int u) 
 }
 
 
-template <int BITS>
+template <int BITS, bool RTN = false>
 __global__ void __launch_bounds__(kSkThreads, 2)
 skinny_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x,
                       const __grid_constant__ CUtensorMap map_p, const SkinnyParams p) {
@@ -208,7 +213,7 @@ skinny_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x,
     asm volatile("prefetch.tensormap [%0];" ::"l"(&map_p) : "memory");
   }
   for (int i = threadIdx.x; i < (1 << BITS); i += kSkThreads) {
-    s_cent[i] = p.centroids[i];
+    s_cent[i] = RTN ? 0.0f : p.centroids[i];
   }
   if (warp == kSkProducerWarp && lane == 0 && T::kPackedByTma) {
     // The packed tiles are fetched 32..64 bytes per row and k step, but L2 fills 256-byte
@@ -227,9 +232,9 @@ skinny_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x,
   // table scale, cleared counters).  A no-op unless launched with programmatic serialization.
   asm volatile("griddepcontrol.wait;" ::: "memory");
   for (int i = threadIdx.x; i < kSkMaxTokens; i += kSkThreads) {
-    s_tok[i] = i < p.rows ? p.row_scale[i] : 0.0f;
+    s_tok[i] = i < p.rows ? (RTN ? 1.0f : p.row_scale[i]) : 0.0f;
   }
-  const float table_scale = p.table_scale != nullptr ? __ldg(p.table_scale) : kCentroidScale;
+  const float table_scale = RTN ? 1.0f : (p.table_scale != nullptr ? __ldg(p.table_scale) : kCentroidScale);
   __syncthreads();
   if (BITS == 6) {
     for (int i = threadIdx.x; i < 64 * 32; i += kSkThreads) {
@@ -286,7 +291,7 @@ skinny_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x,
     }
   } else if (warp == kSkMmaWarp) {
     if (lane == 0) {
-      const uint32_t idesc = instr_desc_tokens(p.n_pad);
+      const uint32_t idesc = instr_desc_tokens(p.n_pad, RTN);
       SkinnyRing copy;
       SkinnyRing slot;
       int local = 0;  // units this CTA has started
@@ -350,6 +355,24 @@ skinny_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x,
       table.hi[q] = hi;
       table.lo[q] = lo;
     }
+    // RTN: the 16 possible values of this row and k step, bf16((i - 8) * scale) as the
+    // reference's CPU kernel rounds them (packed_adaln_cpu.cpp:61-73)
+    auto rtn_table = [&](float scale) {
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        uint32_t hi = 0;
+        uint32_t lo = 0;
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const uint32_t bits = __bfloat16_as_ushort(
+              __float2bfloat16_rn(__fmul_rn(static_cast<float>(4 * q + e - 8), scale)));
+          hi |= (bits >> 8) << (8 * e);
+          lo |= (bits & 0xffu) << (8 * e);
+        }
+        table.hi[q] = hi;
+        table.lo[q] = lo;
+      }
+    };
     const uint16_t *lane_lut = s_lut + (BITS == 6 ? lane : (lane & 7));
     const uint32_t row_off = (row >> 3) * 1024 + (row & 7) * 128;
     SkinnyRing copy;
@@ -374,12 +397,21 @@ skinny_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x,
       if (!T::kPackedByTma) {
         load_global(0, words);
       }
+      // RTN: this row's scale of every k step, fetched one step ahead
+      const __nv_bfloat16 *scale_row =
+          RTN ? p.rtn_scales + (row_valid ? n_global : 0) * p.k_iters + unit.it_begin : nullptr;
+      float scale_now = RTN ? __bfloat162float(scale_row[0]) : 0.0f;
       for (int it = 0; it < unit.iters; ++it) {
         const int s = copy.index;
         const int w = slot.index;
         uint32_t next_words[kWords];
         if (!T::kPackedByTma) {
           load_global(it + 1, next_words);
+        }
+        float scale_next = 0.0f;
+        if (RTN) {
+          scale_next = it + 1 < unit.iters ? __bfloat162float(scale_row[it + 1]) : 0.0f;
+          rtn_table(scale_now);
         }
         if (!mbar_wait(full_bar(s), copy.phase, s_abort, 14)) {
           ok = false;
@@ -450,6 +482,7 @@ skinny_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x,
             words[q] = next_words[q];
           }
         }
+        scale_now = scale_next;
         fence_proxy_async_smem();
         __syncwarp();
         if (lane == 0) {
@@ -472,7 +505,7 @@ skinny_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x,
       float scale_n = 0.0f;
       float bias_n = 0.0f;
       if (n_ok) {
-        scale_n = __fdiv_rn(__bfloat162float(p.row_norms[n]), table_scale);
+        scale_n = RTN ? 1.0f : __fdiv_rn(__bfloat162float(p.row_norms[n]), table_scale);
         bias_n = p.bias_dtype >= 0 ? load_bias(p.bias, p.bias_dtype, n) : 0.0f;
       }
       if (!mbar_wait(acc_full_bar(buf), (local >> 1) & 1u, s_abort, 15)) {
@@ -599,14 +632,14 @@ inline size_t skinny_partial_bytes(const SkinnyPlan &plan, int64_t out_features)
              : 0;
 }
 
-template <int BITS>
+template <int BITS, bool RTN = false>
 int launch_skinny_bits(const CUtensorMap &map_x, const CUtensorMap &map_p, SkinnyParams p,
                        int sm_count, cudaStream_t stream) {
   using T = SkinnyTile<BITS>;
   static std::once_flag once;
   static cudaError_t attr_status = cudaSuccess;
   std::call_once(once, [] {
-    attr_status = cudaFuncSetAttribute(skinny_tcgen05_kernel<BITS>,
+    attr_status = cudaFuncSetAttribute(skinny_tcgen05_kernel<BITS, RTN>,
                                        cudaFuncAttributeMaxDynamicSharedMemorySize,
                                        232448);
   });
@@ -634,7 +667,7 @@ int launch_skinny_bits(const CUtensorMap &map_x, const CUtensorMap &map_p, Skinn
   attr[0].val.programmaticStreamSerializationAllowed = 1;
   config.attrs = attr;
   config.numAttrs = 1;
-  OQ_CHECK_CUDA(cudaLaunchKernelEx(&config, skinny_tcgen05_kernel<BITS>, map_x, map_p, p));
+  OQ_CHECK_CUDA(cudaLaunchKernelEx(&config, skinny_tcgen05_kernel<BITS, RTN>, map_x, map_p, p));
   count_launch();
   return OQ_OK;
 }

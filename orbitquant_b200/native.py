@@ -54,6 +54,9 @@ _SIGNATURES = {
     "oq_quantize_weight": (_int, [_vp, _int, _i64, _i64, _vp, _vp, _i64, _vp, _vp, _int, _f32, _vp, _vp,
                                   _vp, _vp, _sz, _vp]),
     "oq_quantize_weight_workspace_bytes": (_sz, [_i64, _i64]),
+    "oq_rtn_int4_linear_forward": (_int, [_vp, _vp, _i64, _i64, _i64, _vp, _i64, _vp, _int, _vp, _int,
+                                          _vp, _sz, _vp]),
+    "oq_rtn_int4_workspace_bytes": (_sz, [_i64, _i64, _i64]),
     "oq_static_scratch_bytes": (_sz, []),
     "oq_linear_workspace_bytes": (_sz, [_i64, _i64, _i64, _int, _int, _int, _int]),
     "oq_gemm_device_status": (_int, [ctypes.POINTER(ctypes.c_int)]),
@@ -382,3 +385,23 @@ def quantize_weight_packed(weight, *, permutation, signs, block_size, boundaries
             _ptr(cent), int(bits), float(eps), _ptr(norms_in), _ptr(norms_out), _ptr(packed),
             _ptr(ws), ws_bytes, _stream(device)))
     return packed, norms_out
+
+
+def rtn_int4_linear_forward(x, packed, scales, bias, *, out_features, group_size=64):
+    """``x @ W^T + bias`` with ``W[n, k] = bf16((code - 8) * scale[n, k // 64])`` decoded from
+    the packed 4-bit codes; bf16 in, bf16 out (the AdaLN modulation layers)."""
+    _require_cuda("x", x)
+    in_features = x.shape[-1]
+    device = x.device
+    x2 = x.to(torch.bfloat16).contiguous().reshape(-1, in_features)
+    rows = x2.shape[0]
+    out = torch.empty((rows, out_features), dtype=torch.bfloat16, device=device)
+    lib = load()
+    ws_bytes = lib.oq_rtn_int4_workspace_bytes(rows, in_features, out_features)
+    ws = torch.empty(max(ws_bytes, 16), dtype=torch.uint8, device=device)
+    bias_code = 0 if bias is None else DTYPE_CODES[bias.dtype]
+    with torch.cuda.device(device):
+        _check(lib.oq_rtn_int4_linear_forward(
+            _ptr(out), _ptr(x2), rows, in_features, out_features, _ptr(packed), packed.numel(),
+            _ptr(scales), int(group_size), _ptr(bias), bias_code, _ptr(ws), ws_bytes, _stream(device)))
+    return out.reshape(*x.shape[:-1], out_features)

@@ -28,6 +28,7 @@ class TinyBlock(torch.nn.Module):
         self.fc1 = torch.nn.Linear(dim, hidden)
         self.fc2 = torch.nn.Linear(hidden, dim)
         self.norm = torch.nn.LayerNorm(dim)      # stays unquantised
+        self.mod = torch.nn.Linear(dim, 6 * dim)  # AdaLN modulation: RTN-INT4
 
 
 class TinyModel(torch.nn.Module):
@@ -40,6 +41,7 @@ class TinyModel(torch.nn.Module):
 QUANTIZED = ["blocks.0.to_q", "blocks.0.proj", "blocks.0.fc1", "blocks.0.fc2",
              "blocks.1.to_q", "blocks.1.proj", "blocks.1.fc1", "blocks.1.fc2"]
 LOW_BITS = {"blocks.1.to_q": 2, "blocks.1.fc1": 3}
+ADALN = ["blocks.0.mod", "blocks.1.mod"]
 
 
 def main(reference_root: str) -> None:
@@ -48,6 +50,7 @@ def main(reference_root: str) -> None:
 
     from orbitquant.artifacts.writer import save_orbitquant_artifact
     from orbitquant.config import OrbitQuantConfig
+    from orbitquant.adaln import RTNInt4Linear
     from orbitquant.layers import OrbitQuantLinear
 
     torch.manual_seed(11)
@@ -69,7 +72,15 @@ def main(reference_root: str) -> None:
         inp = h if linear.in_features == 192 else x
         with torch.no_grad():
             forward[name] = quantized(inp).float().numpy()
-    summary = SimpleNamespace(quantized_modules=list(QUANTIZED), skipped_modules=["head"], adaln_modules=[])
+    for name in ADALN:
+        parent = model.get_submodule(name.rsplit(".", 1)[0])
+        child = name.rsplit(".", 1)[1]
+        quantized = RTNInt4Linear.from_linear(getattr(parent, child), config=config, module_name=name)
+        setattr(parent, child, quantized)
+        with torch.no_grad():
+            forward[name] = quantized(x).float().numpy()
+    summary = SimpleNamespace(quantized_modules=list(QUANTIZED), skipped_modules=["head"],
+                              adaln_modules=list(ADALN))
     if OUT.exists():
         shutil.rmtree(OUT)
     save_orbitquant_artifact(model, OUT, config=config, source_model_id="synthetic/tiny",

@@ -24,6 +24,7 @@ class TinyBlock(torch.nn.Module):
         self.fc1 = torch.nn.Linear(dim, hidden)
         self.fc2 = torch.nn.Linear(hidden, dim)
         self.norm = torch.nn.LayerNorm(dim)
+        self.mod = torch.nn.Linear(dim, 6 * dim)
 
 
 class TinyModel(torch.nn.Module):
@@ -50,6 +51,13 @@ def test_load_replaces_modules_and_reads_bytes_exactly():
         assert (module.bias is None) == (f"{name}.bias" not in stored)
         keys = {k for k in model.state_dict() if k.startswith(name + ".")}
         assert {k[len(name) + 1:] for k in keys} <= {"bias", "packed_weight_indices", "row_norms"}
+    from orbitquant_b200.adaln import RTNInt4Linear
+    for name in manifest["adaln_modules"]:
+        module = model.get_submodule(name)
+        assert isinstance(module, RTNInt4Linear)
+        assert torch.equal(module.packed_weight, stored[f"{name}.packed_weight"])
+        assert torch.equal(module.scales, stored[f"{name}.scales"])
+    assert len(manifest["adaln_modules"]) == 2
     assert model.get_submodule("blocks.1.to_q").weight_bits == 2
     assert model.get_submodule("blocks.1.fc1").weight_bits == 3
 
@@ -102,6 +110,10 @@ def test_loaded_modules_reproduce_the_reference_forward():
     ref = np.load(ARTIFACT / "reference_forward.npz")
     x = torch.from_numpy(ref["x"].copy()).view(torch.bfloat16).to(dev)
     h = torch.from_numpy(ref["h"].copy()).view(torch.bfloat16).to(dev)
+    for name in manifest["adaln_modules"]:
+        y = model.get_submodule(name)(x).float().cpu()
+        expect = torch.from_numpy(ref[name.replace(".", "__")])
+        assert float((y - expect).norm() / expect.norm()) < 4e-3, name
     for name in manifest["quantized_modules"]:
         module = model.get_submodule(name)
         assert module.packed_weight_indices.device.type == "cuda"
