@@ -439,6 +439,9 @@ def main():
     parser.add_argument("--no-cpu-baseline", action="store_true")
     parser.add_argument("--gather", default="epilogue", choices=["epilogue", "nccl"],
                         help="multi-GPU: how column shards are reassembled")
+    parser.add_argument("--shard", default="n", choices=["n", "m"],
+                        help="multi-GPU: n = output features sharded (the default; outputs gathered), "
+                             "m = tokens sharded (every rank holds all weights, no collective)")
     parser.add_argument("--rows", type=int, default=0,
                         help="override the workload's token count (profiling on a smaller case)")
     args = parser.parse_args()
@@ -469,14 +472,19 @@ def main():
         return
 
     warmup = max(3, args.warmup)
-    rows, layers, w_bits, a_bits = build_layers(args.workload, device, rank, world, args.rows)
+    token_sharded = distributed and args.shard == "m"
+    rows, layers, w_bits, a_bits = build_layers(args.workload, device, rank, 1 if token_sharded else world,
+                                                args.rows)
+    global_rows = rows
+    if token_sharded:
+        rows = global_rows // world + (1 if rank < global_rows % world else 0)
     inputs = [synth_activations(rows, k, WORKLOADS[args.workload][3] * 1000 + i).to(device)
               for i, (_n, k, _N, _g, _m) in enumerate(layers)]
 
     # Column shards are reassembled either by the GEMM epilogue itself (each finished tile is
     # stored into every rank's full-width buffer over NVLink; one inter-rank barrier follows)
     # or, with --gather nccl, by an all-gather collective after the kernel.
-    fused_gather = distributed and args.gather == "epilogue" and rows > 128
+    fused_gather = distributed and not token_sharded and args.gather == "epilogue" and rows > 128
     peers = {}
     gather_note = None
     if fused_gather:
@@ -497,7 +505,7 @@ def main():
 
     def sharded_forward(i, x, want_full):
         _name, _k, n, _g, module = layers[i]
-        if not (distributed and want_full):
+        if not (distributed and want_full) or token_sharded:
             return module(x)
         if fused_gather:
             peers[i].scatter(module, x)
@@ -533,7 +541,7 @@ def main():
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         elapsed_ms = float(t.item())
     ms_per_step = elapsed_ms / args.steps
-    total_flops = sum(layer_flops(rows, k, n) for _n, k, n, _g, _m in layers)
+    total_flops = sum(layer_flops(global_rows, k, n) for _n, k, n, _g, _m in layers)
     value = total_flops / (ms_per_step * 1e-3) / 1e12
 
     # ---- dominant kernel alone: the packed-weight GEMM on pre-quantised activations ----
@@ -658,12 +666,13 @@ def main():
             "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "bf16",
             "data": "synthetic",
             "config": {
-                "workload": (f"{args.workload}: OrbitLinear W{w_bits}A{a_bits} bf16, M={rows}, "
+                "workload": (f"{args.workload}: OrbitLinear W{w_bits}A{a_bits} bf16, M={global_rows}, "
                              + ", ".join(f"{n_} {k}->{n}" for n_, k, n, _g, _m in layers)),
                 "l2": "per-step working set (inputs+weights+outputs) exceeds the 126 MB L2; no flush",
-                "parallelism": f"n_shard{world}" if distributed else "single",
+                "parallelism": (f"m_shard{world}" if token_sharded else f"n_shard{world}") if distributed else "single",
                 "gather": ("gemm epilogue stores into every rank's buffer (peer memory), one barrier"
-                           if fused_gather else (gather_note or "nccl all_gather_into_tensor")) if distributed else None,
+                           if fused_gather else ("none (token-sharded)" if token_sharded else
+                                                 (gather_note or "nccl all_gather_into_tensor"))) if distributed else None,
                 "weight_mode": "centroid (f16 centroid operand, row norm in the epilogue)",
             },
             "roofline": roofline,
