@@ -39,7 +39,7 @@ constexpr int kSkMmaWarp = kSkExpanderWarps + 1;
 constexpr int kSkEpilogueWarp0 = kSkExpanderWarps + 2;
 constexpr int kSkThreads = (kSkExpanderWarps + 2 + 4) * 32;
 constexpr int kSkMaxTokens = 128;
-constexpr int kSkMinItersPerSplit = 8;
+constexpr int kSkMinItersPerSplit = 12;  // measured: 12 beats 8 and 16 on 3072-wide layers at 16 tokens
 
 template <int BITS>
 struct SkinnyTile {
@@ -606,9 +606,17 @@ inline SkinnyPlan skinny_plan(int64_t rows, int64_t in_features, int64_t out_fea
   plan.n_tiles = static_cast<int>((out_features + kSkRows - 1) / kSkRows);
   const int k_iters = static_cast<int>(in_features / kBK);
   // at least two units per resident CTA, with at least kSkMinItersPerSplit k steps each
-  const int wanted = 4 * sm_count;
+  int per_sm = 4;
+  if (const char *env = getenv("ORBIT_B200_SKINNY_UNITS_PER_SM")) {  // tuning only
+    per_sm = atoi(env) > 0 ? atoi(env) : per_sm;
+  }
+  const int wanted = per_sm * sm_count;
   int splits = (wanted + plan.n_tiles - 1) / plan.n_tiles;
-  int most = k_iters / kSkMinItersPerSplit > 0 ? k_iters / kSkMinItersPerSplit : 1;
+  int min_iters = kSkMinItersPerSplit;
+  if (const char *env = getenv("ORBIT_B200_SKINNY_MIN_ITERS")) {  // tuning only
+    min_iters = atoi(env) > 0 ? atoi(env) : min_iters;
+  }
+  int most = k_iters / min_iters > 0 ? k_iters / min_iters : 1;
   // every slice writes (and the reduction re-reads) n_pad x 128 fp32 partial sums per unit:
   // keep that traffic under about half of the packed weight bytes
   const int64_t traffic_cap = in_features / (32 * static_cast<int64_t>(plan.n_pad));
