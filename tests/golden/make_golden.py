@@ -1,7 +1,7 @@
 """Generate the committed golden fixtures from the REFERENCE implementation.
 
 Run where the reference checkout is present (it is imported read-only from
-``$ORBITQUANT_REFERENCE_ROOT/src``, default ``/root/reference/src``) and where
+``$ORBITQUANT_REFERENCE_ROOT/src``) and where
 ``oracle/_ref`` has been built (``python oracle/build_ref.py``):
 
     python tests/golden/make_golden.py
