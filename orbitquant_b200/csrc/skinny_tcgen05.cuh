@@ -355,22 +355,32 @@ skinny_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x,
       table.hi[q] = hi;
       table.lo[q] = lo;
     }
-    // RTN: the 16 possible values of this row and k step, bf16((i - 8) * scale) as the
-    // reference's CPU kernel rounds them (packed_adaln_cpu.cpp:61-73)
-    auto rtn_table = [&](float scale) {
+    // RTN: the table holds the integers -8 .. 7 as bf16 (exact); a decoded pair is then
+    // multiplied by the row's scale of this k step with one bf16x2 multiply.  (i - 8) * scale
+    // is exact in fp32 (a 4-bit integer times an 8-bit significand), so the single rounding of
+    // mul.rn.bf16x2 equals the reference's bf16((i - 8) * scale) (packed_adaln_cpu.cpp:61-73).
+    if (RTN) {
 #pragma unroll
       for (int q = 0; q < 4; ++q) {
         uint32_t hi = 0;
         uint32_t lo = 0;
 #pragma unroll
         for (int e = 0; e < 4; ++e) {
-          const uint32_t bits = __bfloat16_as_ushort(
-              __float2bfloat16_rn(__fmul_rn(static_cast<float>(4 * q + e - 8), scale)));
+          const uint32_t bits = __bfloat16_as_ushort(__float2bfloat16_rn(static_cast<float>(4 * q + e - 8)));
           hi |= (bits >> 8) << (8 * e);
           lo |= (bits & 0xffu) << (8 * e);
         }
         table.hi[q] = hi;
         table.lo[q] = lo;
+      }
+    }
+    auto rtn_scale = [&](uint4 &v, uint32_t scale2) {
+      const __nv_bfloat162 sc = *reinterpret_cast<const __nv_bfloat162 *>(&scale2);
+      uint32_t *w = reinterpret_cast<uint32_t *>(&v);
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const __nv_bfloat162 prod = __hmul2(*reinterpret_cast<const __nv_bfloat162 *>(&w[e]), sc);
+        w[e] = *reinterpret_cast<const uint32_t *>(&prod);
       }
     };
     const uint16_t *lane_lut = s_lut + (BITS == 6 ? lane : (lane & 7));
@@ -400,7 +410,7 @@ skinny_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x,
       // RTN: this row's scale of every k step, fetched one step ahead
       const __nv_bfloat16 *scale_row =
           RTN ? p.rtn_scales + (row_valid ? n_global : 0) * p.k_iters + unit.it_begin : nullptr;
-      float scale_now = RTN ? __bfloat162float(scale_row[0]) : 0.0f;
+      uint32_t scale_now = RTN ? __bfloat16_as_ushort(scale_row[0]) : 0u;
       for (int it = 0; it < unit.iters; ++it) {
         const int s = copy.index;
         const int w = slot.index;
@@ -408,10 +418,9 @@ skinny_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x,
         if (!T::kPackedByTma) {
           load_global(it + 1, next_words);
         }
-        float scale_next = 0.0f;
+        uint32_t scale_next = 0u;
         if (RTN) {
-          scale_next = it + 1 < unit.iters ? __bfloat162float(scale_row[it + 1]) : 0.0f;
-          rtn_table(scale_now);
+          scale_next = it + 1 < unit.iters ? __bfloat16_as_ushort(scale_row[it + 1]) : 0u;
         }
         if (!mbar_wait(full_bar(s), copy.phase, s_abort, 14)) {
           ok = false;
@@ -466,6 +475,9 @@ skinny_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x,
             decode8_lut<6, 32>(lo, hi, lane_lut, expanded[c]);
           } else {
             decode8_lut<8, 8>(lo, hi, lane_lut, expanded[c]);
+          }
+          if (RTN) {
+            rtn_scale(expanded[c], scale_now | (scale_now << 16));
           }
         }
 #pragma unroll
