@@ -97,6 +97,9 @@ __global__ void __launch_bounds__(kMaxWarps * 32) small_rows_w4_kernel(const Sma
     }
   }
   __syncthreads();
+  // Launched with programmatic stream serialization: the table above was built while the
+  // kernel that produces the activations was still running; its output is read from here on.
+  asm volatile("griddepcontrol.wait;" ::: "memory");
 
   float acc[kMaxNB][4];
 #pragma unroll
@@ -245,10 +248,20 @@ int launch_small_rows(void *out, const void *x, int dtype, int64_t rows, int64_t
   const int grid = static_cast<int>((out_features + 8 * nb - 1) / (8 * nb));
   const bool scaled = weight_mode == OQ_WEIGHT_BF16_SCALED;
   const size_t smem = (scaled ? 64 : 256 * kLutRep * 8) + static_cast<size_t>(warps) * nb * 128 * 4;
+  cudaLaunchConfig_t config = {};
+  config.gridDim = dim3(grid);
+  config.blockDim = dim3(warps * 32);
+  config.dynamicSmemBytes = smem;
+  config.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  config.attrs = attr;
+  config.numAttrs = 1;
   if (scaled) {
-    small_rows_w4_kernel<true><<<grid, warps * 32, smem, stream>>>(p);
+    OQ_CHECK_CUDA(cudaLaunchKernelEx(&config, small_rows_w4_kernel<true>, p));
   } else {
-    small_rows_w4_kernel<false><<<grid, warps * 32, smem, stream>>>(p);
+    OQ_CHECK_CUDA(cudaLaunchKernelEx(&config, small_rows_w4_kernel<false>, p));
   }
   OQ_CHECK_CUDA(cudaGetLastError());
   count_launch();
