@@ -116,8 +116,9 @@ class PeerOutput:
         self.out_features = out_features
         self.tensor = symm_mem.empty((rows, out_features), dtype=torch.bfloat16, device=device)
         self.handle = symm_mem.rendezvous(self.tensor, self.group)
-        # own copy first: the local store is the one the next layer reads soonest
-        order = [self.rank] + [r for r in range(self.world) if r != self.rank]
+        # own copy first (the next layer reads it soonest), then the peers starting from the
+        # next rank, so that at any moment the ranks store into different destinations
+        order = [(self.rank + i) % self.world for i in range(self.world)]
         self.ptrs = [int(self.handle.buffer_ptrs[r]) for r in order]
         self.lo, self.hi = shard_bounds(out_features, self.world, self.rank)
 
