@@ -437,7 +437,7 @@ def main():
     parser.add_argument("--impl", default="ours", choices=["ours", "reference"])
     parser.add_argument("--workload", default="dit_block", choices=sorted(WORKLOADS))
     parser.add_argument("--no-cpu-baseline", action="store_true")
-    parser.add_argument("--gather", default="epilogue", choices=["epilogue", "nccl"],
+    parser.add_argument("--gather", default="epilogue", choices=["epilogue", "dma", "nccl"],
                         help="multi-GPU: how column shards are reassembled")
     parser.add_argument("--shard", default="n", choices=["n", "m"],
                         help="multi-GPU: n = output features sharded (the default; outputs gathered), "
@@ -484,7 +484,9 @@ def main():
     # Column shards are reassembled either by the GEMM epilogue itself (each finished tile is
     # stored into every rank's full-width buffer over NVLink; one inter-rank barrier follows)
     # or, with --gather nccl, by an all-gather collective after the kernel.
-    fused_gather = distributed and not token_sharded and args.gather == "epilogue" and rows > 128
+    fused_gather = distributed and not token_sharded and args.gather in ("epilogue", "dma") and rows > 128
+    dma_gather = fused_gather and args.gather == "dma"
+    copy_stream = torch.cuda.Stream() if dma_gather else None
     peers = {}
     gather_note = None
     if fused_gather:
@@ -503,10 +505,15 @@ def main():
             peers = {}
             gather_note = gather_note or "a peer could not map symmetric memory; NCCL all-gather used"
 
-    def sharded_forward(i, x, want_full):
+    def sharded_forward(i, x, want_full, defer_wait=False):
         _name, _k, n, _g, module = layers[i]
         if not (distributed and want_full) or token_sharded:
             return module(x)
+        if dma_gather:
+            peers[i].scatter_dma(module, x, copy_stream)
+            if not defer_wait:
+                peers[i].wait()
+            return peers[i].tensor
         if fused_gather:
             peers[i].scatter(module, x)
             peers[i].wait()
@@ -514,7 +521,14 @@ def main():
         return gather_columns(module(x), n)
 
     def step():
-        return [sharded_forward(i, x, layers[i][3]) for i, x in enumerate(inputs)]
+        # the four projections are independent here, so with the copy-engine gather each
+        # layer's transfers run under the next layer's kernels and are joined at the end
+        outs = [sharded_forward(i, x, layers[i][3], defer_wait=True) for i, x in enumerate(inputs)]
+        if dma_gather:
+            for i, layer in enumerate(layers):
+                if layer[3]:
+                    peers[i].wait()
+        return outs
 
     def barrier():
         if distributed:
@@ -670,7 +684,8 @@ def main():
                              + ", ".join(f"{n_} {k}->{n}" for n_, k, n, _g, _m in layers)),
                 "l2": "per-step working set (inputs+weights+outputs) exceeds the 126 MB L2; no flush",
                 "parallelism": (f"m_shard{world}" if token_sharded else f"n_shard{world}") if distributed else "single",
-                "gather": ("gemm epilogue stores into every rank's buffer (peer memory), one barrier"
+                "gather": (("copy engines (cudaMemcpy2DAsync into every rank's buffer) under the next layer's kernels, barriers at the end of the step"
+                            if dma_gather else "gemm epilogue stores into every rank's buffer (peer memory), one barrier")
                            if fused_gather else ("none (token-sharded)" if token_sharded else
                                                  (gather_note or "nccl all_gather_into_tensor"))) if distributed else None,
                 "weight_mode": "centroid (f16 centroid operand, row norm in the epilogue)",

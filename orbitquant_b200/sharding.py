@@ -127,6 +127,35 @@ class PeerOutput:
             raise ValueError("module is not this rank's column shard of the output")
         module.forward_scatter(x, self.ptrs, self.out_features, self.lo)
 
+    def scatter_dma(self, module, x: torch.Tensor, copy_stream: "torch.cuda.Stream") -> None:
+        """The rank's shard computed by the ordinary forward, then copied into every rank's
+        buffer by the copy engines (one strided ``cudaMemcpy2DAsync`` per destination on
+        ``copy_stream``): the transfers use no SM and run under whatever the compute stream does
+        next.  ``wait()`` joins them."""
+        from cuda.bindings import runtime as cudart
+
+        if module.out_features != self.hi - self.lo:
+            raise ValueError("module is not this rank's column shard of the output")
+        y = module(x).reshape(-1, module.out_features)
+        ready = torch.cuda.Event()
+        ready.record()
+        with torch.cuda.stream(copy_stream):
+            copy_stream.wait_event(ready)
+            width = y.shape[1] * 2
+            for ptr in self.ptrs:
+                (err,) = cudart.cudaMemcpy2DAsync(
+                    ptr + self.lo * 2, self.out_features * 2, y.data_ptr(), width, width, y.shape[0],
+                    cudart.cudaMemcpyKind.cudaMemcpyDeviceToDevice, copy_stream.cuda_stream)
+                if err != cudart.cudaError_t.cudaSuccess:
+                    raise RuntimeError(f"cudaMemcpy2DAsync failed: {err}")
+            self._copied = torch.cuda.Event()
+            self._copied.record(copy_stream)
+        y.record_stream(copy_stream)
+
     def wait(self) -> None:
         """Every rank's stores into this rank's copy have landed (and this rank's into theirs)."""
+        copied = getattr(self, "_copied", None)
+        if copied is not None:
+            torch.cuda.current_stream().wait_event(copied)
+            self._copied = None
         self.handle.barrier()

@@ -82,7 +82,15 @@ def _two_rank_worker(rank, world, port, result):
         peer.scatter(shard, x)
         peer.wait()
         torch.cuda.synchronize()
-        result[rank] = bool(torch.equal(peer.tensor, gathered)) and native.gemm_device_status() == 0
+        fused_ok = bool(torch.equal(peer.tensor, gathered))
+        # the same gather by the copy engines
+        peer.tensor.fill_(-3.0)
+        peer.wait()
+        peer.scatter_dma(shard, x, torch.cuda.Stream())
+        peer.wait()
+        torch.cuda.synchronize()
+        dma_ok = bool(torch.equal(peer.tensor, gathered))
+        result[rank] = fused_ok and dma_ok and native.gemm_device_status() == 0
     finally:
         dist.destroy_process_group()
 
