@@ -265,6 +265,28 @@ def test_library_exports_every_declared_symbol():
     assert native.load().oq_abi_version() == 1
 
 
+def test_header_is_plain_c_and_links(tmp_path):
+    """The boundary is a C ABI: the header must compile as C99 and a C program must link
+    against the library without any C++ or torch symbol."""
+    import shutil
+    import subprocess
+    gcc = shutil.which("gcc")
+    if gcc is None:
+        pytest.skip("no gcc")
+    source = tmp_path / "use.c"
+    source.write_text('#include "orbit_b200.h"\n'
+                      'int main(void) {\n'
+                      '  if (oq_abi_version() != OQ_ABI_VERSION) return 1;\n'
+                      '  if (oq_unpack_lowbit(0, 9, 4, 0, 0) != OQ_ERR_INVALID) return 2;\n'
+                      '  return oq_last_error()[0] == 0 ? 3 : 0;\n'
+                      '}\n')
+    lib = native.library_path()
+    exe = tmp_path / "use"
+    subprocess.run([gcc, "-std=c99", "-Wall", "-Werror", f"-I{REPO / 'include'}", str(source), str(lib),
+                    f"-Wl,-rpath,{lib.parent}", "-o", str(exe)], check=True)
+    assert subprocess.run([str(exe)]).returncode == 0
+
+
 def test_argument_errors_surface_without_a_gpu():
     lib = native.load()
     assert lib.oq_unpack_lowbit(None, 9, 4, None, None) == -1
