@@ -50,7 +50,7 @@ WORKLOADS = {
 # workload; filled from the summaries under profiles/ (None until captured).
 NCU_TRAFFIC_BYTES = {
     # profiles/gemm_w4_tcgen05_dit_block_traffic.md: mean over the four projections
-    "dit_block": 126.0e6,
+    "dit_block": 97.5e6,
     "video_dit": None,
     "vit_decode": None,
 }
