@@ -14,9 +14,9 @@
 //   tile -> local `full[s]`; its expanders write its half of the f16 weight tile and arrive
 //   on the LEADER's `bready[s]` (16 arrivals: 8 local warps + 8 of the peer, the peer's
 //   through mapa + a cluster-scope mbarrier arrive); the leader's MMA thread issues 2 x 4
-//   MMAs and commits with multicast to both CTAs' `empty[s]` (and, at the end, `acc_full`).
+//   MMAs and one tcgen05.commit arrives on both CTAs' `empty[s]` (and, at the end, `acc_full`).
 //
-// Bulk tensor loads carry no multicast.  Waits are bounded as in the single-CTA kernel; the
+// Every TMA load is an ordinary per-CTA load into the issuing CTA's own shared memory.  Waits are bounded as in the single-CTA kernel; the
 // two cluster-wide barriers (after barrier init, before tensor-memory release) are hardware
 // barriers that every thread of both CTAs reaches on every path.
 
