@@ -16,9 +16,10 @@
 //   through mapa + a cluster-scope mbarrier arrive); the leader's MMA thread issues 2 x 4
 //   MMAs and one tcgen05.commit arrives on both CTAs' `empty[s]` (and, at the end, `acc_full`).
 //
-// Every TMA load is an ordinary per-CTA load into the issuing CTA's own shared memory.  Waits are bounded as in the single-CTA kernel; the
-// two cluster-wide barriers (after barrier init, before tensor-memory release) are hardware
-// barriers that every thread of both CTAs reaches on every path.
+// Every TMA load is an ordinary per-CTA load into the issuing CTA's own shared memory.
+// Waits are bounded as in the single-CTA kernel; the two cluster-wide barriers (after barrier
+// init, before tensor-memory release) are hardware barriers that every thread of both CTAs
+// reaches on every path.
 
 template <int BITS>
 struct PairTile {
