@@ -73,6 +73,16 @@ const char *oq_last_error(void);
  * (monotonic; used by the benchmark to report its own launch count). */
 uint64_t oq_launch_count(void);
 
+/* Tuning switches for tests and profiling (no counterpart in the reference, whose kernels
+ * read ORBITQUANT_MMA64_{DISABLE,FORCE}_PIPELINE from the environment at every launch,
+ * packed_matmul.cu:22-38).  Each switch starts from the environment variable
+ * ORBIT_B200_<NAME>, read once per process, and is changed afterwards only through this
+ * call; value -1 returns the decision to the library.  Names (case-insensitive): tile_n
+ * (128|192|256), tile_order (0|1), skinny (0|1), stream_rows (0|1), prologue_rows (1..8),
+ * skinny_units_per_sm, skinny_min_iters, fused_decode (0|1), prologue_kernel (0|1|2).
+ * Process-wide and not synchronised with launches in flight on other threads. */
+int oq_set_tunable(const char *name, int value);
+
 /* ---- bit stream --------------------------------------------------------------------- */
 
 /* Unpack `count` little-endian `bits`-wide fields of `packed` into one byte each.
@@ -169,6 +179,13 @@ int oq_rows_to_f16_operand(const void *x, int dtype, int64_t rows, int64_t dim, 
 
 /* ---- the whole quantized-linear forward --------------------------------------------- */
 
+/* Names of the kernels oq_linear_forward launches for a problem (static string; "a + b" =
+ * two launches).  The reference reports the same decision after the fact through
+ * OrbitQuantLinear.last_effective_runtime_mode / last_activation_kernel_backend
+ * (src/orbitquant/layers.py:1079-1455); here it can be asked up front. */
+const char *oq_linear_kernel_name(int64_t rows, int64_t in_features, int64_t out_features,
+                                  int weight_bits, int dtype, int weight_mode, int kernel);
+
 /* y = OrbitQuantLinear(x): oq_quantize_activations into workspace, then
  * oq_matmul_packed_weight.  Replaces OrbitQuantLinear._forward_impl on CUDA
  * (src/orbitquant/layers.py:1079-1455), i.e. the body of the custom op
@@ -261,8 +278,12 @@ int oq_linear_forward_scatter(void *const *outs, int n_outs, int64_t out_ld, int
  *    16384 features); larger problems return OQ_ERR_WORKSPACE with a message and run nothing.
  *  - Cost: every GPU on which the library is loaded holds the 4 MiB until the process exits.
  *  - The first call on each device looks the array's device address up
- *    (cudaGetSymbolAddress, with that device current) and caches it; make that first call
+ *    (cudaGetSymbolAddress, with that device current) and caches it.  That lookup may load
+ *    the library's device code on that device and allocate inside the driver, so make one
+ *    warm-up call per device at start-up: outside the region that must not allocate and
  *    before any stream capture begins.
+ *  - The cached address does not survive cudaDeviceReset or any other re-creation of the
+ *    device's primary context; do not use this entry point in a process after that.
  *  - All calls on a device share the one array, which keeps the previous call's contents.
  *    Nothing in it needs clearing between calls (each call overwrites all it reads), but two
  *    calls that overlap on the GPU (different streams, or concurrent graph branches) race

@@ -37,7 +37,10 @@ OUT_DIR = HERE / "_ref"
 
 
 def reference_root() -> Path:
-    return Path(os.environ.get("ORBITQUANT_REFERENCE_ROOT", "/root/reference"))
+    """The reference checkout: ``$ORBITQUANT_REFERENCE_ROOT``, else a directory named
+    ``reference`` beside this repository."""
+    env = os.environ.get("ORBITQUANT_REFERENCE_ROOT")
+    return Path(env) if env else HERE.parent.parent / "reference"
 
 
 def build(verbose: bool = False) -> Path | None:

@@ -1,6 +1,8 @@
 // extern "C" surface of liborbit_b200.so: argument validation, kernel choice, status.
 #include <cstdlib>
 #include <cstring>
+#include <strings.h>
+#include <mutex>
 
 #include "common.cuh"
 
@@ -8,6 +10,30 @@ namespace oq {
 
 thread_local char g_last_error[512] = "";
 std::atomic<uint64_t> g_launch_count{0};
+
+namespace {
+const char *const kTunableNames[OQ_TUNE_COUNT] = {
+    "TILE_N", "TILE_ORDER", "SKINNY", "STREAM_ROWS", "PROLOGUE_ROWS", "SKINNY_UNITS_PER_SM",
+    "SKINNY_MIN_ITERS", "FUSED_DECODE", "PROLOGUE_KERNEL"};
+std::atomic<int> g_tunables[OQ_TUNE_COUNT];
+std::once_flag g_tunables_once;
+
+void init_tunables() {
+  std::call_once(g_tunables_once, [] {
+    for (int i = 0; i < OQ_TUNE_COUNT; ++i) {
+      char name[64];
+      snprintf(name, sizeof(name), "ORBIT_B200_%s", kTunableNames[i]);
+      const char *env = std::getenv(name);
+      g_tunables[i].store(env == nullptr ? -1 : std::atoi(env), std::memory_order_relaxed);
+    }
+  });
+}
+}  // namespace
+
+int tunable(int which) {
+  init_tunables();
+  return g_tunables[which].load(std::memory_order_relaxed);
+}
 
 int fail(int status, const char *format, ...) {
   va_list args;
@@ -84,8 +110,6 @@ int launch_tcgen05_rtn_int4(void *out, const void *x_bf16, int64_t rows, int64_t
 int read_gemm_status(int *status);
 int clear_gemm_status();
 
-namespace {
-
 // The kernels are built for sm_100a only; refuse anything else before a launch fails with
 // "no kernel image".
 int check_device() {
@@ -105,6 +129,8 @@ int check_device() {
   return OQ_OK;
 }
 
+namespace {
+
 int resolve_weight_mode(int weight_mode) {
   return weight_mode == OQ_WEIGHT_AUTO ? OQ_WEIGHT_CENTROID : weight_mode;
 }
@@ -112,11 +138,10 @@ int resolve_weight_mode(int weight_mode) {
 size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
 
 // Within the tcgen05 family: up to 128 rows go to the operand-swapped few-token kernel.
-// ORBIT_B200_SKINNY=0 keeps them on the large-row kernel (for A/B timing).
+// The skinny tunable set to 0 keeps them on the large-row kernel (for A/B timing).
 bool use_skinny(int64_t rows, int64_t in_features, int64_t out_features, int bits, int dtype, int mode) {
-  const char *env = std::getenv("ORBIT_B200_SKINNY");
-  const bool enabled = env == nullptr || std::atoi(env) != 0;
-  return enabled && tcgen05_skinny_supported(rows, in_features, out_features, bits, dtype, mode);
+  return tunable(OQ_TUNE_SKINNY) != 0 &&
+         tcgen05_skinny_supported(rows, in_features, out_features, bits, dtype, mode);
 }
 
 // Kernel for a problem: the caller's explicit choice, or by shape.
@@ -144,12 +169,9 @@ int choose_kernel(int kernel, int64_t rows, int64_t in_features, int64_t out_fea
 }
 
 // Within the small-rows family: large layers go to the persistent streaming kernel.
-// ORBIT_B200_STREAM_ROWS=0 / 1 forces one or the other (for A/B timing).
+// The stream_rows tunable set to 0 / 1 forces one or the other (for A/B timing).
 bool use_stream_rows(int64_t rows, int64_t in_features, int64_t out_features, int bits, int dtype) {
-  static const int forced = [] {
-    const char *env = std::getenv("ORBIT_B200_STREAM_ROWS");
-    return env == nullptr ? -1 : std::atoi(env);
-  }();
+  const int forced = tunable(OQ_TUNE_STREAM_ROWS);
   if (forced == 0) {
     return false;
   }
@@ -226,6 +248,18 @@ int oq_abi_version(void) { return OQ_ABI_VERSION; }
 const char *oq_last_error(void) { return g_last_error; }
 
 uint64_t oq_launch_count(void) { return g_launch_count.load(std::memory_order_relaxed); }
+
+int oq_set_tunable(const char *name, int value) {
+  OQ_CHECK_ARG(name != nullptr, "null tunable name");
+  init_tunables();
+  for (int i = 0; i < OQ_TUNE_COUNT; ++i) {
+    if (strcasecmp(name, kTunableNames[i]) == 0) {
+      g_tunables[i].store(value, std::memory_order_relaxed);
+      return OQ_OK;
+    }
+  }
+  return fail(OQ_ERR_INVALID, "unknown tunable '%s'", name);
+}
 
 int oq_unpack_lowbit(const uint8_t *packed, int bits, int64_t count, uint8_t *values, void *stream) {
   OQ_CHECK_ARG(bits >= 1 && bits <= 8, "bits must be in [1, 8]");
@@ -430,6 +464,26 @@ size_t oq_linear_workspace_bytes(int64_t rows, int64_t in_features, int64_t out_
                                    kernel == OQ_KERNEL_AUTO ? OQ_KERNEL_AUTO : kernel);
 }
 
+const char *oq_linear_kernel_name(int64_t rows, int64_t in_features, int64_t out_features,
+                                  int weight_bits, int dtype, int weight_mode, int kernel) {
+  if (rows <= 0 || in_features <= 0 || out_features <= 0) {
+    return "none";
+  }
+  const int mode = resolve_weight_mode(weight_mode);
+  switch (choose_kernel(kernel, rows, in_features, out_features, weight_bits, dtype, mode)) {
+    case OQ_KERNEL_SMALL_ROWS:
+      return use_stream_rows(rows, in_features, out_features, weight_bits, dtype)
+                 ? "rotate_quantize + stream_rows_w4_kernel"
+                 : "rotate_quantize + small_rows_w4_kernel";
+    case OQ_KERNEL_TCGEN05:
+      return use_skinny(rows, in_features, out_features, weight_bits, dtype, mode)
+                 ? "rotate_quantize + skinny_tcgen05_kernel"
+                 : "rotate_quantize + gemm_w4_tcgen05_kernel";
+    default:
+      return "rotate_quantize + tiled_matmul_kernel";
+  }
+}
+
 int oq_linear_forward(void *out, const void *x, int dtype, int64_t rows, int64_t in_features,
                       int64_t out_features, const uint8_t *packed, int64_t packed_bytes,
                       int weight_bits, const void *row_norms_bf16, const float *weight_centroids,
@@ -443,6 +497,7 @@ int oq_linear_forward(void *out, const void *x, int dtype, int64_t rows, int64_t
   OQ_CHECK_ARG(weight_mode >= OQ_WEIGHT_AUTO && weight_mode <= OQ_WEIGHT_BF16_SCALED,
                "unknown weight_mode %d", weight_mode);
   OQ_CHECK_ARG(kernel >= OQ_KERNEL_AUTO && kernel <= OQ_KERNEL_TCGEN05, "unknown kernel %d", kernel);
+  OQ_CHECK_ARG(bias == nullptr || valid_dtype(bias_dtype), "bias must be float32, float16, or bfloat16");
   const int64_t needed = (out_features * in_features * weight_bits + 7) / 8;
   OQ_CHECK_ARG(packed_bytes >= needed, "packed weights are too short");
   if (rows == 0 || out_features == 0) {
@@ -505,6 +560,7 @@ int oq_linear_forward_scatter(void *const *outs, int n_outs, int64_t out_ld, int
                               void *stream) {
   OQ_CHECK_ARG(outs != nullptr, "null output list");
   OQ_CHECK_ARG(valid_dtype(dtype), "x must be float32, float16, or bfloat16");
+  OQ_CHECK_ARG(bias == nullptr || valid_dtype(bias_dtype), "bias must be float32, float16, or bfloat16");
   OQ_CHECK_ARG(rows >= 0 && in_features > 0 && out_features >= 0, "negative or empty shape");
   OQ_CHECK_ARG(weight_bits >= 1 && weight_bits <= 8, "bits must be in [1, 8]");
   const int64_t needed = (out_features * in_features * weight_bits + 7) / 8;

@@ -23,6 +23,26 @@ int fail(int status, const char *format, ...);
 
 inline void count_launch(uint64_t n = 1) { g_launch_count.fetch_add(n, std::memory_order_relaxed); }
 
+// Tuning switches for tests and profiling.  Process-wide; each starts from the environment
+// variable ORBIT_B200_<NAME> (read once, when the first switch is looked up) and can be
+// changed afterwards with oq_set_tunable().  -1 = not set: the library decides by shape.
+enum {
+  OQ_TUNE_TILE_N = 0,            // large-row tcgen05 kernel: output tile width 128 | 192 | 256
+  OQ_TUNE_TILE_ORDER,            // 1 = column tiles fastest, 0 = row tiles fastest
+  OQ_TUNE_SKINNY,                // 0 = rows <= 128 stay on the large-row tcgen05 kernel
+  OQ_TUNE_STREAM_ROWS,           // 0 / 1 = never / always the persistent small-rows kernel
+  OQ_TUNE_PROLOGUE_ROWS,         // tokens per CTA of the general rotate-and-quantize kernel
+  OQ_TUNE_SKINNY_UNITS_PER_SM,   // few-token kernel: work units per SM
+  OQ_TUNE_SKINNY_MIN_ITERS,      // few-token kernel: fewest k steps per reduction slice
+  OQ_TUNE_FUSED_DECODE,          // 0 = rows <= 16 never take the single-launch fused kernel
+  OQ_TUNE_PROLOGUE_KERNEL,       // 0 = general, 1 = multi-token CTA, 2 = warp-per-block kernel
+  OQ_TUNE_COUNT
+};
+int tunable(int which);
+
+// OQ_OK when the current device is an sm_100 part, OQ_ERR_DEVICE otherwise.
+int check_device();
+
 #define OQ_CHECK_ARG(cond, ...)                         \
   do {                                                  \
     if (!(cond)) {                                      \

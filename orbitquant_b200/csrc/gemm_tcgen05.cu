@@ -51,11 +51,6 @@ constexpr int kBK = 64;
 constexpr int kEpilogueWarps = 8;  // two accumulators x four TMEM lane quarters
 constexpr float kCentroidScale = kTableScaleBase;  // table scale when none was searched
 constexpr uint32_t kSpinLimit = 1u << 22;
-// Rate of the CTA-pair kernel relative to the 256-wide single-CTA tile.  Measured 0.89 (fc1
-// 3072->12288 at 4608 rows: 1040 against 1164 TFLOP/s): halving the decode does not pay
-// because the tensor pipe is held back by shared-memory operand reads, which a pair does not
-// reduce, and the pair adds a cross-CTA hop to every stage hand-over.  0 keeps it opt-in.
-constexpr double kPairRate = 0.0;
 
 template <int BN, int BITS>
 struct Tile {
@@ -118,7 +113,6 @@ struct GemmParams {
   // tile).  The second keeps DRAM traffic minimal when the activations do not fit in L2: every
   // activation row tile is then read once while the whole weight matrix stays L2-resident.
   int columns_fastest;
-  int debug_skip;  // profiling only (ORBIT_B200_DEBUG_SKIP): 1 = expanders skip the decode
 };
 
 // ---- PTX wrappers ------------------------------------------------------------------------
@@ -629,7 +623,7 @@ gemm_w4_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
         }
       }
 #pragma unroll
-      for (int c = 0; c < (p.debug_skip ? 0 : kGroups); ++c) {
+      for (int c = 0; c < kGroups; ++c) {
         const int chunk = part * kGroups + c;
         const uint32_t dst = dst_row + (((chunk ^ (row & 7)) & 7) << 4);
         asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(dst), "r"(expanded[c].x),
@@ -848,7 +842,6 @@ int launch_bn(const CUtensorMap &map_a, const CUtensorMap &map_p, const GemmPara
   return OQ_OK;
 }
 
-#include "gemm_pair_tcgen05.cuh"
 #include "skinny_tcgen05.cuh"
 
 }  // namespace
@@ -952,39 +945,15 @@ int launch_tcgen05_gemm_scatter(void *const *outs, int n_outs, int64_t out_ld, i
   if (score(128, 0.76) > best) {
     bn = 128;
   }
-  // ORBIT_B200_TILE_N=128|192|256 pins the width (tests and profiling).
-  if (const char *forced = getenv("ORBIT_B200_TILE_N")) {
-    const int value = atoi(forced);
+  // the tile_n tunable (128 | 192 | 256) pins the width (tests and profiling)
+  {
+    const int value = tunable(OQ_TUNE_TILE_N);
     if (value == 128 || value == 192 || value == 256) {
       bn = value;
     }
   }
-  // A pair of CTAs (cta_group::2) on a 512 x 256 tile halves the decode work per MMA; it
-  // wins when its grid fills the machine about as well.  ORBIT_B200_PAIR=0 / 1 pins the choice.
-  const int64_t m_pairs = (rows + 2 * kBM - 1) / (2 * kBM);
-  const int64_t pair_tiles = m_pairs * ((out_features + 255) / 256);
-  bool use_pair = false;
-  {
-    const int64_t ctas = 2 * pair_tiles;
-    const int64_t waves = (ctas + sm_count - 1) / sm_count;
-    const double useful_n = static_cast<double>(out_features) /
-                            static_cast<double>(((out_features + 255) / 256) * 256);
-    const double useful_m = static_cast<double>(rows) / static_cast<double>(m_pairs * 2 * kBM);
-    const double single_useful_m = static_cast<double>(rows) / static_cast<double>(m_tiles * kBM);
-    const double pair_score = kPairRate * useful_n * useful_m * static_cast<double>(ctas) /
-                              static_cast<double>(waves * sm_count);
-    const double single_score = std::max(best, score(bn, bn == 256 ? 1.0 : (bn == 192 ? 0.93 : 0.76))) *
-                                single_useful_m;
-    use_pair = pair_score > single_score;
-  }
-  if (const char *forced = getenv("ORBIT_B200_PAIR")) {
-    use_pair = atoi(forced) != 0;
-  }
-  if (use_pair) {
-    bn = 128;  // the packed tensor map's box: the 128 weight rows one CTA of the pair expands
-  }
   const int64_t n_tiles = (out_features + bn - 1) / bn;
-  OQ_CHECK_ARG(m_tiles * n_tiles < (1ll << 31) && pair_tiles < (1ll << 30), "too many output tiles");
+  OQ_CHECK_ARG(m_tiles * n_tiles < (1ll << 31), "too many output tiles");
 
   CUtensorMap map_a;
   CUtensorMap map_p;
@@ -1046,22 +1015,8 @@ int launch_tcgen05_gemm_scatter(void *const *outs, int n_outs, int64_t out_ld, i
   const int64_t act_bytes = rows * in_features * 2;
   const int64_t weight_bytes = out_features * in_features * bits / 8;
   p.columns_fastest = (weight_bytes > (int64_t(96) << 20) && act_bytes < weight_bytes) ? 0 : 1;
-  if (const char *order = getenv("ORBIT_B200_TILE_ORDER")) {  // 0 / 1 pins it (profiling)
-    p.columns_fastest = atoi(order) != 0 ? 1 : 0;
-  }
-  if (const char *skip = getenv("ORBIT_B200_DEBUG_SKIP")) {
-    p.debug_skip = atoi(skip);
-  }
-  if (use_pair) {
-    p.m_tiles = static_cast<int>(m_pairs);
-    const int pairs = static_cast<int>(pair_tiles);
-    switch (bits) {
-      case 2: return launch_pair_bits<2>(map_a, map_p, p, pairs, stream);
-      case 3: return launch_pair_bits<3>(map_a, map_p, p, pairs, stream);
-      case 4: return launch_pair_bits<4>(map_a, map_p, p, pairs, stream);
-      case 6: return launch_pair_bits<6>(map_a, map_p, p, pairs, stream);
-      default: return launch_pair_bits<8>(map_a, map_p, p, pairs, stream);
-    }
+  if (tunable(OQ_TUNE_TILE_ORDER) >= 0) {  // 0 / 1 pins it (profiling)
+    p.columns_fastest = tunable(OQ_TUNE_TILE_ORDER) != 0 ? 1 : 0;
   }
   const int grid = static_cast<int>(m_tiles * n_tiles);
   switch (bits) {
@@ -1161,9 +1116,6 @@ int launch_tcgen05_skinny(void *out, const void *x, const float *row_scale, cons
   p.splits = plan.splits;
   p.chunk_iters = plan.chunk_iters;
   p.n_tiles = plan.n_tiles;
-  if (const char *skip = getenv("ORBIT_B200_DEBUG_SKIP")) {
-    p.debug_skip = atoi(skip);
-  }
   if (plan.splits > 1) {
     const size_t need = skinny_partial_bytes(plan, out_features);
     if (workspace == nullptr || workspace_bytes < need) {

@@ -524,8 +524,8 @@ int launch_rotate_quantize(const void *x, int x_dtype, int64_t rows, int64_t dim
       break;
     }
   }
-  if (const char *forced = getenv("ORBIT_B200_PROLOGUE_ROWS")) {  // profiling only
-    const int value = atoi(forced);
+  {
+    const int value = tunable(OQ_TUNE_PROLOGUE_ROWS);  // profiling only
     if (value >= 1 && value <= 8 && value <= rows) {
       rows_per_cta = value;
     }

@@ -87,7 +87,6 @@ struct SkinnyParams {
   int copy_stages;         // ring of packed + activation tiles
   int copy_stage_bytes;
   int slots;               // ring of expanded weight tiles
-  int debug_skip;          // profiling only: 1 = expanders skip the decode
   // RTN-INT4 group-64 weights (the AdaLN modulation layers): value = bf16((code - 8) * scale),
   // one bf16 scale per weight row and 64-wide k step; both MMA operands are then bf16.
   const __nv_bfloat16 *rtn_scales;  // [out_features][k_iters]
@@ -481,7 +480,7 @@ skinny_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x,
           }
         }
 #pragma unroll
-        for (int c = 0; c < (p.debug_skip ? 0 : kGroups); ++c) {
+        for (int c = 0; c < kGroups; ++c) {
           const int chunk = part * kGroups + c;
           const uint32_t dst = dst_row + (((chunk ^ (row & 7)) & 7) << 4);
           asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(dst), "r"(expanded[c].x),
@@ -619,14 +618,14 @@ inline SkinnyPlan skinny_plan(int64_t rows, int64_t in_features, int64_t out_fea
   const int k_iters = static_cast<int>(in_features / kBK);
   // at least two units per resident CTA, with at least kSkMinItersPerSplit k steps each
   int per_sm = 4;
-  if (const char *env = getenv("ORBIT_B200_SKINNY_UNITS_PER_SM")) {  // tuning only
-    per_sm = atoi(env) > 0 ? atoi(env) : per_sm;
+  if (tunable(OQ_TUNE_SKINNY_UNITS_PER_SM) > 0) {
+    per_sm = tunable(OQ_TUNE_SKINNY_UNITS_PER_SM);
   }
   const int wanted = per_sm * sm_count;
   int splits = (wanted + plan.n_tiles - 1) / plan.n_tiles;
   int min_iters = kSkMinItersPerSplit;
-  if (const char *env = getenv("ORBIT_B200_SKINNY_MIN_ITERS")) {  // tuning only
-    min_iters = atoi(env) > 0 ? atoi(env) : min_iters;
+  if (tunable(OQ_TUNE_SKINNY_MIN_ITERS) > 0) {
+    min_iters = tunable(OQ_TUNE_SKINNY_MIN_ITERS);
   }
   int most = k_iters / min_iters > 0 ? k_iters / min_iters : 1;
   // every slice writes (and the reduction re-reads) n_pad x 128 fp32 partial sums per unit:

@@ -2,12 +2,18 @@
 //
 // oq_linear_forward needs a caller-provided workspace for the quantised activations that
 // travel from the rotate-and-quantize kernel to the matmul kernel.  Some callers have no
-// way to provide one: code that runs inside another runtime's enqueue callback (an
-// inference-engine plugin, a stream-ordered host callback) where cudaMalloc and every
-// allocating library routine are off limits, and C programs that hand the GPU's whole
-// memory to one pool at start-up and have no allocator left on the hot path.  For them this
-// file holds the workspace itself, as a fixed-size device array that is part of the loaded
-// library image.
+// way to provide one: code that runs inside another runtime's enqueue method (an
+// inference-engine plugin), where cudaMalloc and every allocating library routine are off
+// limits, and C programs that hand the GPU's whole memory to one pool at start-up and have
+// no allocator left on the hot path.  For them this file holds the workspace itself, as a
+// fixed-size device array that is part of the loaded library image.
+//
+// The first call on a device looks the array's address up (cudaGetSymbolAddress), which may
+// load the library's device code on that device and so may allocate inside the driver: make
+// one warm-up call per device at start-up, outside the region that must not allocate and
+// before any stream capture.  The address is cached per device index for the life of the
+// process; after cudaDeviceReset (or any re-creation of the device's primary context) the
+// cached address is stale and this entry point must not be used again in that process.
 #include <mutex>
 
 #include "common.cuh"
@@ -73,12 +79,16 @@ int oq_linear_forward_static(void *out, const void *x, int dtype, int64_t rows, 
                 "with a caller-provided workspace instead",
                 need, kStaticScratchBytes);
   }
+  if (int rc = check_device()) {  // before the symbol lookup: a foreign device gets OQ_ERR_DEVICE
+    return rc;
+  }
   void *scratch = nullptr;
   if (int rc = static_scratch_for_current_device(&scratch)) {
     return rc;
   }
-  // Nothing in the scratch has to start at zero: the first kernel overwrites every byte the
-  // second one reads (activations and per-token factors of exactly `rows` tokens).
+  // Nothing in the scratch has to start at zero on entry: the first kernel overwrites every
+  // byte the second one reads (activations and per-token factors of exactly `rows` tokens)
+  // and clears the reduction-slice counters the few-token kernel keeps there.
   return oq_linear_forward(out, x, dtype, rows, in_features, out_features, packed, packed_bytes,
                            weight_bits, row_norms_bf16, weight_centroids, bias, bias_dtype, perm,
                            signs, block, act_boundaries, act_centroids, act_bits, eps, weight_mode,

@@ -30,6 +30,7 @@ _SIGNATURES = {
     "oq_abi_version": (ctypes.c_int, []),
     "oq_last_error": (ctypes.c_char_p, []),
     "oq_launch_count": (ctypes.c_uint64, []),
+    "oq_set_tunable": (_int, [ctypes.c_char_p, _int]),
     "oq_unpack_lowbit": (_int, [_vp, _int, _i64, _vp, _vp]),
     "oq_pack_lowbit": (_int, [_vp, _int, _i64, _vp, _vp]),
     "oq_dequantize_weight": (_int, [_vp, _int, _i64, _i64, _vp, _vp, _vp, _int, _vp]),
@@ -59,6 +60,7 @@ _SIGNATURES = {
     "oq_rtn_int4_workspace_bytes": (_sz, [_i64, _i64, _i64]),
     "oq_static_scratch_bytes": (_sz, []),
     "oq_linear_workspace_bytes": (_sz, [_i64, _i64, _i64, _int, _int, _int, _int]),
+    "oq_linear_kernel_name": (ctypes.c_char_p, [_i64, _i64, _i64, _int, _int, _int, _int]),
     "oq_gemm_device_status": (_int, [ctypes.POINTER(ctypes.c_int)]),
     "oq_gemm_clear_device_status": (_int, []),
 }
@@ -120,6 +122,19 @@ def _stream(device: torch.device):
 
 def launch_count() -> int:
     return int(load().oq_launch_count())
+
+
+def set_tunable(name: str, value: int | None) -> None:
+    """Pin (or, with ``None``, release) one of the library's tuning switches; see
+    ``oq_set_tunable`` in ``include/orbit_b200.h``.  For tests and profiling."""
+    _check(load().oq_set_tunable(name.encode(), -1 if value is None else int(value)))
+
+
+def forward_kernel_name(rows: int, in_features: int, out_features: int, weight_bits: int, *,
+                        dtype=torch.bfloat16, weight_mode=WEIGHT_AUTO, kernel=KERNEL_AUTO) -> str:
+    """Which kernels ``linear_forward`` launches for this problem (``oq_linear_kernel_name``)."""
+    return load().oq_linear_kernel_name(rows, in_features, out_features, weight_bits,
+                                        DTYPE_CODES[dtype], weight_mode, kernel).decode()
 
 
 def gemm_device_status() -> int:

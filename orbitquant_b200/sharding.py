@@ -100,6 +100,16 @@ class PeerOutput:
     GEMM epilogue (each finished tile is stored into all ranks' copies over NVLink);
     ``wait()`` is the inter-rank barrier after which ``tensor`` holds every shard.
 
+    Reuse rule.  The object owns TWO buffers and alternates between them: round ``i`` (one
+    ``scatter`` + ``wait``) fills buffer ``i % 2``, and ``tensor`` is the buffer of the last
+    completed round.  A peer may start round ``i + 2`` -- which overwrites the buffer of
+    round ``i`` on THIS rank -- only after it has passed the barrier of round ``i + 1``,
+    i.e. after this rank's stream has reached its own ``wait()`` of round ``i + 1``.  So the
+    result of a round stays valid, on every rank, until that rank calls ``wait()`` for the
+    next round, provided its reads were enqueued on the same stream before that call (a
+    consumer on another stream must be joined first).  With a single buffer a fast rank's
+    next epilogue could overwrite a slow peer's copy while that peer still reads it.
+
     Plain peer stores only: no multicast object is created, so a rank that dies does not
     take the others' NVLink down with it."""
 
@@ -114,18 +124,24 @@ class PeerOutput:
         self.world = dist.get_world_size(self.group)
         self.rank = dist.get_rank(self.group)
         self.out_features = out_features
-        self.tensor = symm_mem.empty((rows, out_features), dtype=torch.bfloat16, device=device)
-        self.handle = symm_mem.rendezvous(self.tensor, self.group)
+        self.buffers = symm_mem.empty((2, rows, out_features), dtype=torch.bfloat16, device=device)
+        self.handle = symm_mem.rendezvous(self.buffers, self.group)
         # own copy first (the next layer reads it soonest), then the peers starting from the
         # next rank, so that at any moment the ranks store into different destinations
         order = [(self.rank + i) % self.world for i in range(self.world)]
-        self.ptrs = [int(self.handle.buffer_ptrs[r]) for r in order]
+        half = rows * out_features * 2
+        self.ptrs = [[int(self.handle.buffer_ptrs[r]) + b * half for r in order] for b in range(2)]
         self.lo, self.hi = shard_bounds(out_features, self.world, self.rank)
+        self.round = 0          # rounds started
+        self.tensor = self.buffers[0]
 
     def scatter(self, module, x: torch.Tensor) -> None:
         if module.out_features != self.hi - self.lo:
             raise ValueError("module is not this rank's column shard of the output")
-        module.forward_scatter(x, self.ptrs, self.out_features, self.lo)
+        slot = self.round % 2
+        self.round += 1
+        self._filling = slot
+        module.forward_scatter(x, self.ptrs[slot], self.out_features, self.lo)
 
     def scatter_dma(self, module, x: torch.Tensor, copy_stream: "torch.cuda.Stream") -> None:
         """The rank's shard computed by the ordinary forward, then copied into every rank's
@@ -137,12 +153,15 @@ class PeerOutput:
         if module.out_features != self.hi - self.lo:
             raise ValueError("module is not this rank's column shard of the output")
         y = module(x).reshape(-1, module.out_features)
+        slot = self.round % 2
+        self.round += 1
+        self._filling = slot
         ready = torch.cuda.Event()
         ready.record()
         with torch.cuda.stream(copy_stream):
             copy_stream.wait_event(ready)
             width = y.shape[1] * 2
-            for ptr in self.ptrs:
+            for ptr in self.ptrs[slot]:
                 (err,) = cudart.cudaMemcpy2DAsync(
                     ptr + self.lo * 2, self.out_features * 2, y.data_ptr(), width, width, y.shape[0],
                     cudart.cudaMemcpyKind.cudaMemcpyDeviceToDevice, copy_stream.cuda_stream)
@@ -159,3 +178,7 @@ class PeerOutput:
             torch.cuda.current_stream().wait_event(copied)
             self._copied = None
         self.handle.barrier()
+        filling = getattr(self, "_filling", None)
+        if filling is not None:
+            self.tensor = self.buffers[filling]
+            self._filling = None

@@ -67,3 +67,22 @@ def rel_l2(a: torch.Tensor, b: torch.Tensor) -> float:
     a = a.double().flatten()
     b = b.double().flatten()
     return float((a - b).norm() / b.norm().clamp_min(1e-30))
+
+
+@pytest.fixture
+def tunables():
+    """Pins tuning switches of the CUDA library for one test and releases them afterwards."""
+    from orbitquant_b200 import native
+
+    class _Tunables:
+        def __init__(self):
+            self.touched = set()
+
+        def set(self, name, value):
+            native.set_tunable(name, value)
+            self.touched.add(name)
+
+    handle = _Tunables()
+    yield handle
+    for name in handle.touched:
+        native.set_tunable(name, None)

@@ -99,4 +99,7 @@ def main(reference_root: str) -> None:
 
 
 if __name__ == "__main__":
-    main(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")
+    import os
+
+    main(sys.argv[1] if len(sys.argv) > 1 else
+         os.environ.get("ORBITQUANT_REFERENCE_ROOT") or str(Path(__file__).resolve().parents[3] / "reference"))

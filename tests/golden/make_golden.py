@@ -26,6 +26,7 @@ from __future__ import annotations
 import hashlib
 import os
 import sys
+import tempfile
 from pathlib import Path
 
 import numpy as np
@@ -33,11 +34,12 @@ import torch
 
 HERE = Path(__file__).resolve().parent
 REPO = HERE.parent.parent
-REF_ROOT = Path(os.environ.get("ORBITQUANT_REFERENCE_ROOT", "/root/reference"))
+REF_ROOT = Path(os.environ.get("ORBITQUANT_REFERENCE_ROOT") or REPO.parent / "reference")
 
 # The reference derives 8-bit tables in minutes; let it keep its own disk cache in a
 # scratch folder so that re-running this script is quick.
-os.environ.setdefault("ORBITQUANT_CODEBOOK_CACHE_DIR", str(REPO / "_work" / "codebook_cache"))
+os.environ.setdefault("ORBITQUANT_CODEBOOK_CACHE_DIR",
+                      str(Path(tempfile.gettempdir()) / "orbitquant_codebook_cache"))
 sys.path.insert(0, str(REF_ROOT / "src"))
 sys.path.insert(0, str(REPO))
 

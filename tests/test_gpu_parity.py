@@ -3,10 +3,15 @@ reference's golden vectors.  Everything here needs a B200.
 
 Tolerances (bf16 activations/outputs):
 * bit streams, activation codes, token norms and quantised activations: bit-exact;
-* matmul / forward outputs: rel-L2 <= 1e-3 and max-abs <= 2e-2 against the oracle evaluated
-  with the SAME weight arithmetic (fp32 centroids for ``centroid`` mode, bf16(c*row_norm)
-  for ``bf16_scaled``); max-abs is judged on outputs scaled to unit RMS because one bf16
-  ulp at |y| >= 4 already exceeds 2e-2.
+* matmul / forward outputs: rel-L2 <= 1e-3 on the bf16 outputs, and max-abs <= 2e-2 in units
+  of the output RMS on the value BEFORE the final bf16 rounding, against the oracle
+  evaluated with the SAME weight arithmetic (fp32 centroids for ``centroid`` mode,
+  bf16(c*row_norm) for ``bf16_scaled``).  The oracle returns its fp32 value before that
+  rounding; the kernels return bf16 only, so the assertion is
+  ``|y_gpu - y_ref_f32| <= 2e-2 * rms + ulp_bf16(y_gpu) / 2`` (the half ulp is the most the
+  device's own final rounding can add).  Where the reference side is rounded too (the
+  compiled reference kernels return bf16), one whole ulp is allowed instead: one bf16 ulp
+  at |y| >= 4 is 0.031, more than the tolerance itself.
 """
 from __future__ import annotations
 
@@ -30,17 +35,45 @@ def _dev():
     return torch.device("cuda", 0)
 
 
-def _check_close(y_gpu: torch.Tensor, y_ref: torch.Tensor, what):
+def bf16_ulp(values: torch.Tensor) -> torch.Tensor:
+    """Spacing of bf16 numbers at the magnitude of ``values`` (8 significant bits)."""
+    mag = values.abs().double().clamp_min(2.0 ** -126)
+    return torch.exp2(torch.floor(torch.log2(mag)) - 7)
+
+
+def parity_errors(y_gpu: torch.Tensor, y_ref):
+    """(rel-L2, max-abs of the rounded outputs, excess of the pre-rounding difference over the
+    half ulp the final rounding may add), the last two in units of the reference's RMS.
+    ``y_ref`` is the reference output, or the oracle's pair (rounded output, fp32 value
+    before the final rounding)."""
+    y_ref, y_ref_f32 = y_ref if isinstance(y_ref, tuple) else (y_ref, None)
     y_gpu = y_gpu.detach().float().cpu()
     y_ref = y_ref.detach().float().cpu()
-    assert y_gpu.shape == y_ref.shape, what
-    assert torch.isfinite(y_gpu).all(), what
-    rms = y_ref.pow(2).mean().sqrt().clamp_min(1e-12)
+    rms = y_ref.pow(2).mean().sqrt().clamp_min(1e-12).double()
     err = rel_l2(y_gpu, y_ref)
-    max_abs = float(((y_gpu - y_ref).abs() / rms).max())
+    max_abs = float(((y_gpu - y_ref).abs().double() / rms).max())
+    if y_ref_f32 is not None:
+        # the device rounds its own fp32 value to bf16 (at most half an ulp away from it)
+        y32 = y_ref_f32.detach().double().cpu()
+        excess = ((y_gpu.double() - y32).abs() - 0.5 * bf16_ulp(y_gpu)).clamp_min(0) / rms
+    else:
+        # both sides are rounded: two values that differ by less than the tolerance before
+        # rounding can land one ulp apart
+        excess = ((y_gpu - y_ref).abs().double() - bf16_ulp(torch.maximum(y_gpu.abs(), y_ref.abs()))
+                  ).clamp_min(0) / rms
+    return err, max_abs, float(excess.max())
+
+
+def _check_close(y_gpu: torch.Tensor, y_ref, what):
+    """rel-L2 <= 1e-3 on the bf16 outputs and max-abs <= 2e-2 (unit RMS) on the values before
+    the final bf16 rounding; see the module docstring."""
+    ref_out = y_ref[0] if isinstance(y_ref, tuple) else y_ref
+    assert y_gpu.shape == ref_out.shape, what
+    assert torch.isfinite(y_gpu.detach().float()).all(), what
+    err, max_abs, pre_rounding = parity_errors(y_gpu, y_ref)
     assert err <= REL_L2_TOL, (what, "rel-L2", err)
-    # unit-RMS max-abs: one bf16 ulp of a 4-sigma output is 2^-7 * 4 / 2 = 1.6e-2
-    assert max_abs <= MAX_ABS_TOL * 4, (what, "max-abs/rms", max_abs)
+    assert pre_rounding <= MAX_ABS_TOL, (what, "max-abs before rounding / rms", pre_rounding,
+                                         "max-abs of the bf16 outputs / rms", max_abs)
 
 
 def _random_layer(k, n, bits, seed, bias=True):
@@ -131,7 +164,7 @@ def test_prologue_other_dtypes(oracle, dtype):
     rot = RPBHRotation(1024, 2, 256)
     cb = get_codebook(1024, 4)
     x = (torch.randn(11, 1024) * 2).to(dtype)
-    ref, codes_ref, _ = oracle.quantize_activations(x, rot.permutation, rot.signs, 256,
+    ref, codes_ref = oracle.quantize_activations(x, rot.permutation, rot.signs, 256,
                                                     cb.boundaries, cb.centroids)
     got, codes = native.quantize_activations(x.to(dev), rot.permutation, rot.signs, cb.centroids,
                                              cb.boundaries, eps=1e-10, block_size=256,
@@ -174,7 +207,7 @@ def test_prologue_empty_and_errors():
 
 def _oracle_matmul(oracle, x, packed, rn, cent, bits, n, bias, mode_name):
     mode = oracle.MM_BF16_LUT if mode_name == "bf16_scaled" else oracle.MM_FP32_CENTROIDS
-    y, _ = oracle.matmul_packed(x, packed, rn, cent, bits=bits, out_features=n, bias=bias, mode=mode)
+    y = oracle.matmul_packed(x, packed, rn, cent, bits=bits, out_features=n, bias=bias, mode=mode)
     return y
 
 
@@ -324,7 +357,7 @@ def test_module_forward_vs_oracle_all_bit_pairs(oracle, golden_codebooks):
         x = x.to(torch.bfloat16)
         y = module(x.to(dev))
         assert y.shape == (2, m // 2, n) and y.dtype == torch.bfloat16
-        ref, _ = oracle.linear_forward(
+        ref = oracle.linear_forward(
             x, module.packed_weight_indices.cpu(), module.row_norms.cpu(),
             None if module.bias is None else module.bias.detach().cpu(),
             perm=module.rotation.permutation, signs=module.rotation.signs,

@@ -90,7 +90,24 @@ def _two_rank_worker(rank, world, port, result):
         peer.wait()
         torch.cuda.synchronize()
         dma_ok = bool(torch.equal(peer.tensor, gathered))
-        result[rank] = fused_ok and dma_ok and native.gemm_device_status() == 0
+        # Reuse: three rounds back to back into one PeerOutput while rank 1 reads slowly.  A
+        # round's result must still be intact when its (delayed) reader runs, although the
+        # fast rank has by then started storing the next round.
+        reuse_ok = True
+        xs = [(torch.randn(rows, k, generator=torch.Generator().manual_seed(20 + i)) * 0.8)
+              .to(torch.bfloat16).to(dev) for i in range(3)]
+        expected = [gather_columns(shard(xi), n) for xi in xs]
+        kept = []
+        for i, xi in enumerate(xs):
+            peer.scatter(shard, xi)
+            peer.wait()
+            if rank == 1:
+                torch.cuda._sleep(200_000_000)   # ~0.1 s: the reader lags behind its peer
+            kept.append(peer.tensor.clone())
+        torch.cuda.synchronize()
+        for got, want in zip(kept, expected):
+            reuse_ok = reuse_ok and bool(torch.equal(got, want))
+        result[rank] = fused_ok and dma_ok and reuse_ok and native.gemm_device_status() == 0
     finally:
         dist.destroy_process_group()
 

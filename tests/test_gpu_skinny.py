@@ -21,7 +21,7 @@ def _case(oracle, rows, k, n, bits, cent, seed, with_bias=True):
     args = dict(bits=bits, out_features=n, in_features=k, bias=bias, kernel=native.KERNEL_TCGEN05)
     y = native.matmul_packed_weight(x.to(dev), packed.to(dev), rn, cent, **args)
     _assert_status_clean()
-    ref, _ = oracle.matmul_packed(x, packed, rn, cent, bits=bits, out_features=n, bias=bias,
+    ref = oracle.matmul_packed(x, packed, rn, cent, bits=bits, out_features=n, bias=bias,
                                   mode=oracle.MM_FP32_CENTROIDS)
     _check_close(y, ref, (rows, k, n, bits))
     again = native.matmul_packed_weight(x.to(dev), packed.to(dev), rn, cent, **args)
@@ -49,7 +49,7 @@ def test_skinny_other_bit_widths(oracle, golden_codebooks, bits, rows):
     _case(oracle, rows, k, n, bits, cent, seed=bits * 13 + rows, with_bias=bits != 3)
 
 
-def test_skinny_agrees_with_large_row_kernel(monkeypatch):
+def test_skinny_agrees_with_large_row_kernel(tunables):
     """Same operands, same f16 products: the two tcgen05 kernels differ only in the order of
     the fp32 accumulation."""
     dev = _dev()
@@ -59,7 +59,7 @@ def test_skinny_agrees_with_large_row_kernel(monkeypatch):
     x = torch.randn(rows, k).to(torch.bfloat16).to(dev)
     args = dict(bits=4, out_features=n, in_features=k, bias=bias, kernel=native.KERNEL_TCGEN05)
     a = native.matmul_packed_weight(x, packed.to(dev), rn, cent, **args)
-    monkeypatch.setenv("ORBIT_B200_SKINNY", "0")
+    tunables.set("skinny", 0)
     b = native.matmul_packed_weight(x, packed.to(dev), rn, cent, **args)
     _assert_status_clean()
     _check_close(a, b, "few-token vs large-row kernel")
@@ -77,7 +77,7 @@ def test_module_forward_decode_batch_on_large_layer(oracle):
     y = q.to(dev)(x.to(dev))
     _assert_status_clean()
     rot, acb, wcb = q.rotation, get_codebook(3072, 4), get_codebook(3072, 4)
-    ref, _ = oracle.linear_forward(x, q.packed_weight_indices.cpu(), q.row_norms.cpu(), q.bias.cpu(),
+    ref = oracle.linear_forward(x, q.packed_weight_indices.cpu(), q.row_norms.cpu(), q.bias.cpu(),
                                    perm=rot.permutation, signs=rot.signs, block=rot.block_size,
                                    act_boundaries=acb.boundaries, act_centroids=acb.centroids,
                                    w_centroids=wcb.centroids, w_bits=4, out_features=3072,
