@@ -53,6 +53,10 @@ class RTNInt4Linear(nn.Module):
             self.register_parameter("bias", None)
         else:
             self.bias = nn.Parameter(bias.detach().clone(), requires_grad=False)
+        # same handle registry as OrbitQuantLinear: the module traces as one opaque node of
+        # the shared custom op, with bf16_output=True (reference adaln.py:312-317)
+        from .layers import _registry_register
+        self._compile_handle = _registry_register(self)
 
     @classmethod
     def from_linear(cls, layer: nn.Module, *, config: OrbitQuantConfig, module_name: str) -> "RTNInt4Linear":
@@ -90,6 +94,12 @@ class RTNInt4Linear(nn.Module):
         return weight[:, : self.in_features].to(dtype)
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
+        if torch.compiler.is_compiling():
+            return torch.ops.orbitquant.packed_linear_forward(
+                x, self._compile_handle, self.out_features, True)
+        return self._forward_impl(x)
+
+    def _forward_impl(self, x: torch.Tensor) -> torch.Tensor:
         if x.device.type != "cuda":
             raise RuntimeError("RTNInt4Linear (orbitquant_b200) requires CUDA input tensors on an "
                                f"sm_100 device; got {x.device.type}. There is no CPU path in this package.")

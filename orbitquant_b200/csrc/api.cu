@@ -85,7 +85,7 @@ int launch_rows_to_f16(const void *x, int dtype, int64_t rows, int64_t dim, void
 int launch_tcgen05_gemm(void *out, const void *x_f16, const float *row_scale,
                         const float *table_scale, int64_t rows, int64_t in_features, int64_t out_features, const uint8_t *packed, int bits,
                         const void *row_norms_bf16, const float *centroids, const void *bias,
-                        int bias_dtype, cudaStream_t stream);
+                        int bias_dtype, cudaStream_t stream, bool scaled = false);
 bool tcgen05_skinny_supported(int64_t rows, int64_t in_features, int64_t out_features, int bits,
                               int dtype, int weight_mode);
 size_t tcgen05_skinny_workspace_bytes(int64_t rows, int64_t in_features, int64_t out_features);
@@ -101,7 +101,7 @@ int launch_tcgen05_gemm_scatter(void *const *outs, int n_outs, int64_t out_ld, i
                                 int64_t rows, int64_t in_features, int64_t out_features,
                                 const uint8_t *packed, int bits, const void *row_norms_bf16,
                                 const float *centroids, const void *bias, int bias_dtype,
-                                cudaStream_t stream);
+                                cudaStream_t stream, bool scaled = false);
 size_t tcgen05_rtn_workspace_bytes(int64_t rows, int64_t in_features, int64_t out_features);
 int launch_tcgen05_rtn_int4(void *out, const void *x_bf16, int64_t rows, int64_t in_features,
                             int64_t out_features, const uint8_t *packed, const void *scales_bf16,
@@ -231,9 +231,10 @@ int tcgen05_matmul(void *out, void *workspace, size_t workspace_bytes, int64_t r
                                  bias_dtype, static_cast<unsigned char *>(workspace) + head,
                                  workspace_bytes - head, s);
   }
+  // bf16_scaled: the operand at the head of the workspace is x_q itself (bf16, not rescaled)
   return launch_tcgen05_gemm(out, workspace, row_scale, table_scale, rows, in_features,
                              out_features, packed, bits, row_norms_bf16, centroids, bias,
-                             bias_dtype, s);
+                             bias_dtype, s, mode == OQ_WEIGHT_BF16_SCALED);
 }
 
 }  // namespace
@@ -378,8 +379,14 @@ int oq_matmul_packed_weight(void *out, const void *x, int dtype, int64_t rows, i
     case OQ_KERNEL_TCGEN05:
       if (!tcgen05_gemm_supported(rows, in_features, out_features, bits, dtype, mode)) {
         return fail(OQ_ERR_UNSUPPORTED,
-                    "the tcgen05 kernel takes bf16 activations, 2/3/4/6/8-bit weights, "
-                    "in_features %% 64 == 0 and the centroid weight mode");
+                    "the tcgen05 kernel takes bf16 activations, in_features %% 64 == 0 and "
+                    "2/3/4/6/8-bit weights (2/3/4-bit in the bf16_scaled weight mode)");
+      }
+      if (mode == OQ_WEIGHT_BF16_SCALED) {
+        // both operands bf16: the caller's activations are the A operand as they are
+        OQ_CHECK_ARG(aligned16(x), "x must be 16-byte aligned");
+        return launch_tcgen05_gemm(out, x, nullptr, nullptr, rows, in_features, out_features, packed,
+                                   bits, row_norms_bf16, centroids, bias, bias_dtype, s, true);
       }
       {
         const size_t need = oq_matmul_workspace_bytes(rows, in_features, out_features, bits, dtype,
@@ -526,10 +533,17 @@ int oq_linear_forward(void *out, const void *x, int dtype, int64_t rows, int64_t
     int zero_count = 0;
     int *zero_words = tcgen05_counters(workspace, rows, in_features, out_features, weight_bits,
                                        dtype, mode, &zero_count);
-    if (int rc = launch_rotate_quantize(x, dtype, rows, in_features, perm, signs, block,
-                                        act_boundaries, act_centroids, act_bits, eps, workspace,
-                                        nullptr, nullptr, row_scale, weight_centroids, weight_bits,
-                                        table_scale, zero_words, zero_count, s)) {
+    if (mode == OQ_WEIGHT_BF16_SCALED) {
+      // x_q in bf16 is the operand; no rescaling, no table scale
+      if (int rc = launch_rotate_quantize(x, dtype, rows, in_features, perm, signs, block,
+                                          act_boundaries, act_centroids, act_bits, eps, workspace,
+                                          nullptr, nullptr, nullptr, nullptr, 0, nullptr, nullptr, 0, s)) {
+        return rc;
+      }
+    } else if (int rc = launch_rotate_quantize(x, dtype, rows, in_features, perm, signs, block,
+                                               act_boundaries, act_centroids, act_bits, eps, workspace,
+                                               nullptr, nullptr, row_scale, weight_centroids, weight_bits,
+                                               table_scale, zero_words, zero_count, s)) {
       return rc;
     }
     return tcgen05_matmul(out, workspace, workspace_bytes, rows, in_features, out_features, packed,

@@ -28,6 +28,12 @@
 //   epilogue           tcgen05.ld of 32 columns at a time, scale by row_norm[n] * 2^-8,
 //                      add bias, round to bf16, 16-byte stores.
 //
+// SCALED variant (2-, 3-, 4-bit): the reference's other weight arithmetic, operand
+// bf16(centroid * row_norm[n]) against the bf16 activations themselves (its AVX512-BF16 CPU
+// kernel and its CUDA kernels).  Every expander thread owns one weight row for the whole k loop,
+// so its register table is simply built from that row's norm; both operands are bf16, nothing
+// is rescaled and the epilogue only adds the bias.
+//
 // Every mbarrier wait is bounded: when a wait gives up it raises the CTA's abort flag
 // and the device status word, every role leaves its loop, in-flight bulk copies are
 // drained (bounded again), tensor memory is released and the kernel returns.
@@ -257,11 +263,12 @@ __device__ __forceinline__ uint64_t smem_desc_k_sw128(uint32_t addr) {
   return desc;
 }
 
-// Instruction descriptor: f32 accumulator, A = B = f16 (format code 0), K-major, M = 128.
-__host__ __device__ constexpr uint32_t instr_desc(int n) {
-  return (1u << 4)                             // D format f32
-         | (0u << 7)                           // A format f16
-         | (0u << 10)                          // B format f16
+// Instruction descriptor: f32 accumulator, A = B = f16 (format code 0) or bf16 (1), K-major,
+// M = 128.
+__host__ __device__ constexpr uint32_t instr_desc(int n, bool bf16_operands = false) {
+  return (1u << 4)                                   // D format f32
+         | ((bf16_operands ? 1u : 0u) << 7)          // A format
+         | ((bf16_operands ? 1u : 0u) << 10)         // B format
          | (static_cast<uint32_t>(n >> 3) << 17)
          | (static_cast<uint32_t>(128 >> 4) << 24);
 }
@@ -365,7 +372,7 @@ __device__ __forceinline__ void group_bits(const uint32_t (&words)[NWORDS], int 
   hi = BITS > 4 ? __funnelshift_r(w1, w2, sh) : 0u;
 }
 
-template <int BN, int BITS>
+template <int BN, int BITS, bool SCALED = false>
 __global__ void __launch_bounds__((Tile<BN, BITS>::kThreads), 1)
 gemm_w4_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
                        const __grid_constant__ CUtensorMap map_p, const GemmParams p) {
@@ -425,7 +432,8 @@ gemm_w4_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
   // (the prologue) is still running; everything below reads that kernel's output.
   asm volatile("griddepcontrol.wait;" ::: "memory");
   // chosen by the kernel that ran just before this one (table_scale.cuh); 2^8 without it
-  const float table_scale = p.table_scale != nullptr ? __ldg(p.table_scale) : kCentroidScale;
+  const float table_scale =
+      SCALED ? 1.0f : (p.table_scale != nullptr ? __ldg(p.table_scale) : kCentroidScale);
   if (BITS == 6) {  // [entry][32 lane copies]
     for (int i = threadIdx.x; i < 64 * 32; i += T::kThreads) {
       s_lut[i] = __half_as_ushort(__float2half_rn(s_cent[i >> 5] * table_scale));
@@ -438,7 +446,7 @@ gemm_w4_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
   for (int i = threadIdx.x; i < BN; i += T::kThreads) {
     const int64_t n = n0 + i;
     const bool ok = n < p.out_features;
-    s_scale[i] = ok ? __fdiv_rn(__bfloat162float(p.row_norms[n]), table_scale) : 0.0f;
+    s_scale[i] = ok ? (SCALED ? 1.0f : __fdiv_rn(__bfloat162float(p.row_norms[n]), table_scale)) : 0.0f;
     s_bias[i] = (ok && p.bias_dtype >= 0) ? load_bias(p.bias, p.bias_dtype, n) : 0.0f;
   }
   tc_fence_before();
@@ -475,7 +483,7 @@ gemm_w4_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
     }
   } else if (warp == T::kMmaWarp) {
     if (lane == 0) {
-      constexpr uint32_t idesc = instr_desc(BN);
+      constexpr uint32_t idesc = instr_desc(BN, SCALED);
       bool ok = true;
       for (int it = 0; it < p.k_iters && ok; ++it) {
         const int s = it % T::kStages;
@@ -509,7 +517,11 @@ gemm_w4_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
     const int et = threadIdx.x;  // expander thread index (every expander warp owns rows)
     const int row = et / kThreadsPerRow;
     const int part = et % kThreadsPerRow;
-    // Register table (2-, 3-, 4-bit): entry i = f16(centroid[i] * 2^8).
+    // Register table (2-, 3-, 4-bit): entry i = f16(centroid[i] * table scale), or, SCALED,
+    // bf16(centroid[i] * row_norm) of the weight row this thread expands.
+    const int64_t table_row = n0 + et / kThreadsPerRow;
+    const float table_norm = (SCALED && table_row < p.out_features)
+                                 ? __bfloat162float(p.row_norms[table_row]) : 0.0f;
     RegTable table;
 #pragma unroll
     for (int q = 0; q < 4; ++q) {
@@ -519,7 +531,9 @@ gemm_w4_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
       for (int e = 0; e < 4; ++e) {
         const int idx = 4 * q + e;
         const float c = (BITS <= 4 && idx < (1 << BITS)) ? s_cent[idx] : 0.0f;
-        const uint32_t bits = __half_as_ushort(__float2half_rn(c * table_scale));
+        const uint32_t bits =
+            SCALED ? static_cast<uint32_t>(__bfloat16_as_ushort(__float2bfloat16_rn(__fmul_rn(c, table_norm))))
+                   : static_cast<uint32_t>(__half_as_ushort(__float2half_rn(c * table_scale)));
         hi |= (bits >> 8) << (8 * e);
         lo |= (bits & 0xffu) << (8 * e);
       }
@@ -658,7 +672,7 @@ gemm_w4_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
       const int quarter = warp & 3;
       const int64_t m_first = m0 + half * 128 + quarter * 32;
       const int64_t m = m_first + lane;
-      const float row_scale = m < p.rows ? p.row_scale[m] : 0.0f;
+      const float row_scale = m < p.rows ? (SCALED ? 1.0f : p.row_scale[m]) : 0.0f;
       unsigned char *park = stage_ptr + warp * (32 * kPitch);
 #pragma unroll 1
       for (int c0 = 0; c0 < BN; c0 += 32) {
@@ -814,13 +828,13 @@ EncodeTiledFn encode_tiled_fn() {
   return fn;
 }
 
-template <int BN, int BITS>
+template <int BN, int BITS, bool SCALED = false>
 int launch_bn(const CUtensorMap &map_a, const CUtensorMap &map_p, const GemmParams &p, int grid,
               cudaStream_t stream) {
   static std::once_flag once;
   static cudaError_t attr_status = cudaSuccess;
   std::call_once(once, [] {
-    attr_status = cudaFuncSetAttribute(gemm_w4_tcgen05_kernel<BN, BITS>,
+    attr_status = cudaFuncSetAttribute(gemm_w4_tcgen05_kernel<BN, BITS, SCALED>,
                                        cudaFuncAttributeMaxDynamicSharedMemorySize,
                                        Tile<BN, BITS>::kSmemBytes);
   });
@@ -837,7 +851,7 @@ int launch_bn(const CUtensorMap &map_a, const CUtensorMap &map_p, const GemmPara
   attr[0].val.programmaticStreamSerializationAllowed = 1;
   config.attrs = attr;
   config.numAttrs = 1;
-  OQ_CHECK_CUDA(cudaLaunchKernelEx(&config, gemm_w4_tcgen05_kernel<BN, BITS>, map_a, map_p, p));
+  OQ_CHECK_CUDA(cudaLaunchKernelEx(&config, gemm_w4_tcgen05_kernel<BN, BITS, SCALED>, map_a, map_p, p));
   count_launch();
   return OQ_OK;
 }
@@ -848,9 +862,12 @@ int launch_bn(const CUtensorMap &map_a, const CUtensorMap &map_p, const GemmPara
 
 bool tcgen05_gemm_supported(int64_t rows, int64_t in_features, int64_t out_features, int bits,
                             int dtype, int weight_mode) {
-  const bool bits_ok = bits == 2 || bits == 3 || bits == 4 || bits == 6 || bits == 8;
+  // bf16(centroid * row_norm) operands need a per-row table: the register-table widths only
+  const bool bits_ok = weight_mode == OQ_WEIGHT_BF16_SCALED
+                           ? (bits == 2 || bits == 3 || bits == 4)
+                           : (bits == 2 || bits == 3 || bits == 4 || bits == 6 || bits == 8);
   return rows > 0 && out_features > 0 && bits_ok && dtype == OQ_DTYPE_BF16 &&
-         weight_mode != OQ_WEIGHT_BF16_SCALED && in_features >= kBK && in_features % kBK == 0 &&
+         in_features >= kBK && in_features % kBK == 0 &&
          in_features <= (1 << 30) && rows < (1ll << 31) && out_features < (1ll << 31);
 }
 
@@ -874,13 +891,13 @@ int launch_rows_to_f16(const void *x, int dtype, int64_t rows, int64_t dim, void
 }
 
 // `x` is the f16 operand [rows, in_features] and `row_scale` its per-token factor.
-template <int BITS>
+template <int BITS, bool SCALED = false>
 int launch_bits(int bn, const CUtensorMap &map_a, const CUtensorMap &map_p, const GemmParams &p,
                 int grid, cudaStream_t stream) {
   switch (bn) {
-    case 256: return launch_bn<256, BITS>(map_a, map_p, p, grid, stream);
-    case 192: return launch_bn<192, BITS>(map_a, map_p, p, grid, stream);
-    default: return launch_bn<128, BITS>(map_a, map_p, p, grid, stream);
+    case 256: return launch_bn<256, BITS, SCALED>(map_a, map_p, p, grid, stream);
+    case 192: return launch_bn<192, BITS, SCALED>(map_a, map_p, p, grid, stream);
+    default: return launch_bn<128, BITS, SCALED>(map_a, map_p, p, grid, stream);
   }
 }
 
@@ -889,16 +906,16 @@ int launch_tcgen05_gemm_scatter(void *const *outs, int n_outs, int64_t out_ld, i
                                 int64_t rows, int64_t in_features, int64_t out_features,
                                 const uint8_t *packed, int bits, const void *row_norms_bf16,
                                 const float *centroids, const void *bias, int bias_dtype,
-                                cudaStream_t stream);
+                                cudaStream_t stream, bool scaled);
 
 int launch_tcgen05_gemm(void *out, const void *x, const float *row_scale, const float *table_scale,
                         int64_t rows, int64_t in_features, int64_t out_features, const uint8_t *packed, int bits,
                         const void *row_norms_bf16, const float *centroids, const void *bias,
-                        int bias_dtype, cudaStream_t stream) {
+                        int bias_dtype, cudaStream_t stream, bool scaled) {
   void *outs[1] = {out};
   return launch_tcgen05_gemm_scatter(outs, 1, out_features, 0, x, row_scale, table_scale, rows,
                                      in_features, out_features, packed, bits, row_norms_bf16,
-                                     centroids, bias, bias_dtype, stream);
+                                     centroids, bias, bias_dtype, stream, scaled);
 }
 
 int launch_tcgen05_gemm_scatter(void *const *outs, int n_outs, int64_t out_ld, int64_t out_col,
@@ -906,8 +923,9 @@ int launch_tcgen05_gemm_scatter(void *const *outs, int n_outs, int64_t out_ld, i
                                 int64_t rows, int64_t in_features, int64_t out_features,
                                 const uint8_t *packed, int bits, const void *row_norms_bf16,
                                 const float *centroids, const void *bias, int bias_dtype,
-                                cudaStream_t stream) {
+                                cudaStream_t stream, bool scaled) {
   OQ_CHECK_ARG(n_outs >= 1 && n_outs <= kMaxOutputs, "1 to %d output buffers", kMaxOutputs);
+  OQ_CHECK_ARG(!scaled || bits <= 4, "the bf16(centroid * row_norm) operand exists for 2-, 3- and 4-bit weights");
   OQ_CHECK_ARG(out_col >= 0 && out_ld >= out_col + out_features,
                "the column range does not fit the leading dimension");
   for (int d = 0; d < n_outs; ++d) {
@@ -1019,6 +1037,13 @@ int launch_tcgen05_gemm_scatter(void *const *outs, int n_outs, int64_t out_ld, i
     p.columns_fastest = tunable(OQ_TUNE_TILE_ORDER) != 0 ? 1 : 0;
   }
   const int grid = static_cast<int>(m_tiles * n_tiles);
+  if (scaled) {
+    switch (bits) {
+      case 2: return launch_bits<2, true>(bn, map_a, map_p, p, grid, stream);
+      case 3: return launch_bits<3, true>(bn, map_a, map_p, p, grid, stream);
+      default: return launch_bits<4, true>(bn, map_a, map_p, p, grid, stream);
+    }
+  }
   switch (bits) {
     case 2: return launch_bits<2>(bn, map_a, map_p, p, grid, stream);
     case 3: return launch_bits<3>(bn, map_a, map_p, p, grid, stream);
@@ -1031,7 +1056,7 @@ int launch_tcgen05_gemm_scatter(void *const *outs, int n_outs, int64_t out_ld, i
 // Few tokens (rows <= 128): the operand-swapped kernel of skinny_tcgen05.cuh.
 bool tcgen05_skinny_supported(int64_t rows, int64_t in_features, int64_t out_features, int bits,
                               int dtype, int weight_mode) {
-  return rows <= kSkMaxTokens &&
+  return rows <= kSkMaxTokens && weight_mode != OQ_WEIGHT_BF16_SCALED &&
          tcgen05_gemm_supported(rows, in_features, out_features, bits, dtype, weight_mode);
 }
 

@@ -164,7 +164,7 @@ def test_prologue_other_dtypes(oracle, dtype):
     rot = RPBHRotation(1024, 2, 256)
     cb = get_codebook(1024, 4)
     x = (torch.randn(11, 1024) * 2).to(dtype)
-    ref, codes_ref = oracle.quantize_activations(x, rot.permutation, rot.signs, 256,
+    ref, codes_ref, _ = oracle.quantize_activations(x, rot.permutation, rot.signs, 256,
                                                     cb.boundaries, cb.centroids)
     got, codes = native.quantize_activations(x.to(dev), rot.permutation, rot.signs, cb.centroids,
                                              cb.boundaries, eps=1e-10, block_size=256,

@@ -190,3 +190,24 @@ def test_module_auto_dispatch_uses_tcgen05(oracle):
         act_centroids=module.activation_codebook.centroids,
         w_centroids=module.weight_codebook.centroids, w_bits=4, out_features=512)
     _check_close(y, ref, "module W4A4 config-1 slice")
+
+
+@pytest.mark.parametrize("bits,rows,k,n", [(4, 300, 1024, 1152), (4, 1000, 3072, 520), (3, 260, 768, 456),
+                                           (2, 515, 768, 456)])
+def test_tcgen05_bf16_scaled_operand(oracle, bits, rows, k, n):
+    """The reference's other weight arithmetic on the tensor cores: operand
+    bf16(centroid * row_norm) against the bf16 activations.  Same operands as the oracle's
+    bf16 table mode, so only the fp32 summation order differs."""
+    dev = _dev()
+    idx, packed, rn, bias = _random_layer(k, n, bits, seed=bits * 7 + rows)
+    cent = get_codebook(k, bits).centroids
+    x = (torch.randn(rows, k) * 0.9).to(torch.bfloat16)
+    native.gemm_clear_device_status()
+    y = native.matmul_packed_weight(x.to(dev), packed.to(dev), rn, cent, bits=bits, out_features=n,
+                                    in_features=k, bias=bias, kernel=native.KERNEL_TCGEN05,
+                                    weight_mode=native.WEIGHT_BF16_SCALED)
+    _assert_status_clean()
+    ref = oracle.matmul_packed(x, packed, rn, cent, bits=bits, out_features=n, bias=bias,
+                               mode=oracle.MM_BF16_LUT)
+    _check_close(y, ref, ("bf16_scaled", bits, rows, k, n))
+    assert rel_l2(y.float().cpu(), ref[0].float()) < 3e-4

@@ -101,3 +101,35 @@ def test_kernel_vs_oracle(oracle, m, k, n, bias):
     assert rel_all <= 4e-3, rel_all      # bf16 output rounding only
     again = q(x.to(dev))
     assert torch.equal(y, again)
+
+
+@pytest.mark.gpu
+def test_compile_fullgraph_with_both_layer_kinds():
+    """A module holding an OrbitQuantLinear and an RTNInt4Linear traces without graph breaks:
+    both go through the one custom op (the AdaLN layer with bf16_output=True) and the
+    compiled result equals eager bit for bit."""
+    if not torch.cuda.is_available():
+        pytest.skip("no CUDA device")
+    from orbitquant_b200 import OrbitQuantConfig, OrbitQuantLinear
+    from orbitquant_b200.adaln import RTNInt4Linear
+
+    dev = torch.device("cuda", 0)
+    torch.manual_seed(11)
+    cfg = OrbitQuantConfig(weight_bits=4, activation_bits=4, rotation_seed=3)
+
+    class Tiny(torch.nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.mod = RTNInt4Linear.from_linear(torch.nn.Linear(256, 512), config=cfg, module_name="mod")
+            self.proj = OrbitQuantLinear.from_linear(torch.nn.Linear(256, 256), config=cfg, module_name="proj")
+
+        def forward(self, x, c):
+            shift, scale = self.mod(c).chunk(2, dim=-1)
+            return self.proj(x * (1 + scale) + shift)
+
+    model = Tiny().to(dev)
+    x = torch.randn(24, 256, device=dev).to(torch.bfloat16)
+    c = torch.randn(24, 256, device=dev).to(torch.bfloat16)
+    eager = model(x, c)
+    compiled = torch.compile(model, fullgraph=True)(x, c)
+    assert compiled.dtype == torch.bfloat16 and torch.equal(compiled, eager)
