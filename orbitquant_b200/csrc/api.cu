@@ -109,6 +109,8 @@ int launch_tcgen05_rtn_int4(void *out, const void *x_bf16, int64_t rows, int64_t
                             size_t workspace_bytes, cudaStream_t stream);
 int read_gemm_status(int *status);
 int clear_gemm_status();
+int read_prologue_status(int *status);
+int clear_prologue_status();
 
 // The kernels are built for sm_100a only; refuse anything else before a launch fails with
 // "no kernel image".
@@ -704,9 +706,24 @@ int oq_rtn_int4_linear_forward(void *out, const void *x_bf16, int64_t rows, int6
 // it synchronises the host with the device; it is meant for tests and debugging.
 int oq_gemm_device_status(int *status) {
   OQ_CHECK_ARG(status != nullptr, "null pointer");
-  return read_gemm_status(status);
+  if (int rc = read_gemm_status(status)) {
+    return rc;
+  }
+  if (*status == 0) {  // the rotate-and-quantize kernel's waits report as 100 + code
+    int prologue = 0;
+    if (int rc = read_prologue_status(&prologue)) {
+      return rc;
+    }
+    *status = prologue != 0 ? 100 + prologue : 0;
+  }
+  return OQ_OK;
 }
 
-int oq_gemm_clear_device_status(void) { return clear_gemm_status(); }
+int oq_gemm_clear_device_status(void) {
+  if (int rc = clear_gemm_status()) {
+    return rc;
+  }
+  return clear_prologue_status();
+}
 
 }  // extern "C"

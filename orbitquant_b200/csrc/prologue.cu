@@ -443,9 +443,44 @@ rotate_quantize_kernel(const PrologueParams p) {
 }  // namespace oq
 
 #include "prologue_fast.cuh"
+#include "prologue_warp.cuh"
 
 namespace oq {
 namespace {
+
+template <bool F16OP>
+void (*warp_kernel_for(int bits))(WarpPrologueParams) {
+  switch (bits) {
+    case 2: return rotate_quantize_warp_kernel<2, F16OP>;
+    case 3: return rotate_quantize_warp_kernel<3, F16OP>;
+    case 4: return rotate_quantize_warp_kernel<4, F16OP>;
+    case 6: return rotate_quantize_warp_kernel<6, F16OP>;
+    case 8: return rotate_quantize_warp_kernel<8, F16OP>;
+    default: return nullptr;
+  }
+}
+
+// Tokens per batch and CTAs per SM of the warp-per-block kernel: two CTAs per SM where the
+// shared memory allows it (latency hiding across CTAs), then as many tokens per batch as fit.
+bool plan_warp_prologue(int dim, int block, int bits, int64_t rows, int max_smem, int *batch_rows,
+                        int *ctas_per_sm, int *smem) {
+  const int shared_per_sm = 228 * 1024;
+  for (int per_sm = 2; per_sm >= 1; --per_sm) {
+    for (int r = kPwMaxRows; r >= 1; r /= 2) {
+      if (r > rows) {
+        continue;
+      }
+      const int total = pw_layout(dim, block, r, bits).total;
+      if (total <= max_smem && per_sm * (total + 1024) <= shared_per_sm) {
+        *batch_rows = r;
+        *ctas_per_sm = per_sm;
+        *smem = total;
+        return true;
+      }
+    }
+  }
+  return false;
+}
 
 template <bool F16OP>
 void (*fast_kernel_for(int bits))(PrologueParams) {
@@ -504,8 +539,54 @@ int launch_rotate_quantize(const void *x, int x_dtype, int64_t rows, int64_t dim
   OQ_CHECK_CUDA(cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, device));
   OQ_CHECK_CUDA(cudaDeviceGetAttribute(&max_smem, cudaDevAttrMaxSharedMemoryPerBlockOptin, device));
 
+  // Kernel choice.  The prologue_kernel tunable pins it: 0 = general, 1 = multi-token CTA,
+  // 2 = warp-per-block; otherwise large token counts take the warp-per-block kernel.
+  const int forced = tunable(OQ_TUNE_PROLOGUE_KERNEL);
+  const bool plain_output = codes == nullptr && norms == nullptr && x_q != nullptr && given_norms == nullptr;
+  if (plain_output && warp_prologue_supported(x_dtype, dim, block, bits) &&
+      (forced == 2 || (forced < 0 && rows >= 2 * static_cast<int64_t>(sm_count)))) {
+    int batch_rows = 0;
+    int ctas_per_sm = 0;
+    int smem_bytes = 0;
+    if (plan_warp_prologue(static_cast<int>(dim), static_cast<int>(block), bits, rows, max_smem,
+                           &batch_rows, &ctas_per_sm, &smem_bytes)) {
+      WarpPrologueParams wp{};
+      wp.x = static_cast<const uint16_t *>(x);
+      wp.xq = static_cast<uint16_t *>(x_q);
+      wp.row_scale = f16_row_scale;
+      wp.perm = perm;
+      wp.signs = signs;
+      wp.boundaries = boundaries;
+      wp.centroids = centroids;
+      wp.rows = rows;
+      wp.dim = static_cast<int>(dim);
+      wp.log2_block = 0;
+      while ((int64_t(1) << wp.log2_block) < block) {
+        ++wp.log2_block;
+      }
+      wp.batch_rows = batch_rows;
+      wp.eps = eps;
+      wp.inv_sqrt_block = static_cast<float>(1.0 / sqrt(static_cast<double>(block)));
+      wp.w_centroids = w_centroids;
+      wp.w_bits = w_bits;
+      wp.table_scale_out = table_scale_out;
+      wp.zero_words = zero_words;
+      wp.zero_count = zero_words != nullptr ? zero_count : 0;
+      void (*wkernel)(WarpPrologueParams) =
+          f16_row_scale != nullptr ? warp_kernel_for<true>(bits) : warp_kernel_for<false>(bits);
+      OQ_CHECK_CUDA(cudaFuncSetAttribute(wkernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes));
+      const int64_t batches = (rows + batch_rows - 1) / batch_rows;
+      const int wgrid = static_cast<int>(std::min<int64_t>(batches, static_cast<int64_t>(sm_count) * ctas_per_sm)) +
+                        (table_scale_out != nullptr ? 1 : 0);
+      wkernel<<<wgrid, kPwThreads, smem_bytes, stream>>>(wp);
+      OQ_CHECK_CUDA(cudaGetLastError());
+      count_launch();
+      return OQ_OK;
+    }
+  }
+
   void (*fast)(PrologueParams) = nullptr;
-  if (x_dtype == OQ_DTYPE_BF16 && dim % 256 == 0 && block >= 256 && codes == nullptr &&
+  if (forced != 0 && x_dtype == OQ_DTYPE_BF16 && dim % 256 == 0 && block >= 256 && codes == nullptr &&
       norms == nullptr && x_q != nullptr) {
     fast = f16_row_scale != nullptr ? fast_kernel_for<true>(bits) : fast_kernel_for<false>(bits);
   }
@@ -648,6 +729,17 @@ int launch_weight_row_norms(const void *w, int dtype, int64_t rows, int64_t dim,
   }
   OQ_CHECK_CUDA(cudaGetLastError());
   count_launch();
+  return OQ_OK;
+}
+
+int read_prologue_status(int *status) {
+  OQ_CHECK_CUDA(cudaMemcpyFromSymbol(status, g_prologue_status, sizeof(int)));
+  return OQ_OK;
+}
+
+int clear_prologue_status() {
+  const int zero = 0;
+  OQ_CHECK_CUDA(cudaMemcpyToSymbol(g_prologue_status, &zero, sizeof(int)));
   return OQ_OK;
 }
 

@@ -23,7 +23,11 @@ __device__ __forceinline__ void clear_words(int *words, int count) {
   }
 }
 
-// Called by all 256 threads of one CTA.  `scratch` holds at least 264 floats of shared memory.
+// Barrier among the 256 searching threads (a named barrier, so that a CTA with more threads
+// than that can leave the others out).
+__device__ __forceinline__ void search_sync() { asm volatile("bar.sync 1, 256;" ::: "memory"); }
+
+// Called by threads 0 .. 255 of one CTA.  `scratch` holds at least 272 floats of shared memory.
 __device__ __forceinline__ void search_table_scale(const float *centroids, int bits, float *out,
                                                    float *scratch) {
   float *s_cent = scratch;
@@ -32,7 +36,7 @@ __device__ __forceinline__ void search_table_scale(const float *centroids, int b
   for (int i = threadIdx.x; i < levels; i += 256) {
     s_cent[i] = centroids[i];
   }
-  __syncthreads();
+  search_sync();
   const int candidates = bits == 8 ? 256 : 1024;
   const int per_thread = candidates / 256;
   const float step = 1.0f / static_cast<float>(candidates);
@@ -61,7 +65,7 @@ __device__ __forceinline__ void search_table_scale(const float *centroids, int b
   if ((threadIdx.x & 31) == 0) {
     s_best[threadIdx.x >> 5] = best;
   }
-  __syncthreads();
+  search_sync();
   if (threadIdx.x == 0) {
     unsigned long long total = s_best[0];
     for (int w = 1; w < 8; ++w) {
@@ -70,7 +74,7 @@ __device__ __forceinline__ void search_table_scale(const float *centroids, int b
     const int cand = static_cast<int>(total & 0xffffffffu);
     *out = kTableScaleBase * (1.0f + static_cast<float>(cand) * step);
   }
-  __syncthreads();
+  search_sync();
 }
 
 }  // namespace oq

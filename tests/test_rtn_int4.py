@@ -124,8 +124,10 @@ def test_compile_fullgraph_with_both_layer_kinds():
             self.proj = OrbitQuantLinear.from_linear(torch.nn.Linear(256, 256), config=cfg, module_name="proj")
 
         def forward(self, x, c):
-            shift, scale = self.mod(c).chunk(2, dim=-1)
-            return self.proj(x * (1 + scale) + shift)
+            # one elementwise op between the two layers: a chain of them would be fused by the
+            # compiler without eager's intermediate bf16 roundings and differ for that reason
+            shift = self.mod(c)[..., :256]
+            return self.proj(x + shift)
 
     model = Tiny().to(dev)
     x = torch.randn(24, 256, device=dev).to(torch.bfloat16)
