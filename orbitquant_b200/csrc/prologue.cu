@@ -460,19 +460,23 @@ void (*warp_kernel_for(int bits))(WarpPrologueParams) {
   }
 }
 
-// Tokens per batch and CTAs per SM of the warp-per-block kernel: two CTAs per SM where the
-// shared memory allows it (latency hiding across CTAs), then as many tokens per batch as fit.
+// Tokens per batch, copy slots and CTAs per SM of the warp-per-block kernel: two CTAs per SM
+// where the shared memory allows it (latency hiding across CTAs), at least three slots (copies
+// must run ahead of the norm warps, which run ahead of the transform warps), then as many
+// tokens per batch as fit.
 bool plan_warp_prologue(int dim, int block, int bits, int64_t rows, int max_smem, int *batch_rows,
-                        int *ctas_per_sm, int *smem) {
+                        int *slots, int *ctas_per_sm, int *smem) {
   const int shared_per_sm = 228 * 1024;
+  static const int kChoices[][2] = {{4, 3}, {2, 4}, {2, 3}, {1, 4}, {1, 3}, {1, 2}};
   for (int per_sm = 2; per_sm >= 1; --per_sm) {
-    for (int r = kPwMaxRows; r >= 1; r /= 2) {
-      if (r > rows) {
+    for (const auto &choice : kChoices) {
+      if (choice[0] > rows) {
         continue;
       }
-      const int total = pw_layout(dim, block, r, bits).total;
+      const int total = pw_layout(dim, block, choice[0], choice[1], bits).total;
       if (total <= max_smem && per_sm * (total + 1024) <= shared_per_sm) {
-        *batch_rows = r;
+        *batch_rows = choice[0];
+        *slots = choice[1];
         *ctas_per_sm = per_sm;
         *smem = total;
         return true;
@@ -546,10 +550,11 @@ int launch_rotate_quantize(const void *x, int x_dtype, int64_t rows, int64_t dim
   if (plain_output && warp_prologue_supported(x_dtype, dim, block, bits) &&
       (forced == 2 || (forced < 0 && rows >= 2 * static_cast<int64_t>(sm_count)))) {
     int batch_rows = 0;
+    int slots = 0;
     int ctas_per_sm = 0;
     int smem_bytes = 0;
     if (plan_warp_prologue(static_cast<int>(dim), static_cast<int>(block), bits, rows, max_smem,
-                           &batch_rows, &ctas_per_sm, &smem_bytes)) {
+                           &batch_rows, &slots, &ctas_per_sm, &smem_bytes)) {
       WarpPrologueParams wp{};
       wp.x = static_cast<const uint16_t *>(x);
       wp.xq = static_cast<uint16_t *>(x_q);
@@ -565,6 +570,7 @@ int launch_rotate_quantize(const void *x, int x_dtype, int64_t rows, int64_t dim
         ++wp.log2_block;
       }
       wp.batch_rows = batch_rows;
+      wp.slots = slots;
       wp.eps = eps;
       wp.inv_sqrt_block = static_cast<float>(1.0 / sqrt(static_cast<double>(block)));
       wp.w_centroids = w_centroids;

@@ -5,12 +5,14 @@
 // the organisation, chosen so that no CTA-wide barrier and no serial phase sits on the
 // critical path:
 //
-//   norm warp (warp 8)      works one batch of R tokens AHEAD of the others: bulk-copies the
-//                           batch into a shared-memory slot (cp.async.bulk, completion on an
-//                           mbarrier), computes the token norms in the reference's AVX-512
-//                           order (16 fused-multiply-add chains per token, two per lane, eight
-//                           lanes per token, then the 8/4/2/1 fold) and tabulates every
-//                           token's possible outputs; then signals `normed[slot]`.
+//   norm warps (8, 9)       work ahead of the others on alternate batches of R tokens: wait
+//                           for the batch's bulk copy (cp.async.bulk into one of S
+//                           shared-memory slots, completion on an mbarrier), compute the
+//                           token norms in the reference's AVX-512 order (16
+//                           fused-multiply-add chains per token, two per lane, eight lanes per
+//                           token, then the 8/4/2/1 fold -- a chain of dim/16 dependent
+//                           operations, which is why there are two such warps) and tabulate
+//                           every token's possible outputs; then signal `normed[slot]`.
 //   transform warps (0..7)  each takes whole 1024-element chunks of a token (one or several
 //                           rotation blocks): lane l gathers the 32 values of positions
 //                           32l .. 32l+31 through a permutation table kept in shared memory
@@ -19,7 +21,13 @@
 //                           store per 4 values, conflict-free reads), runs widths 32 .. 512,
 //                           quantises, and the 2 KB of results leave by one bulk store.  For
 //                           blocks of 2048 / 4096 a team of 2 / 4 warps shares a block and a
-//                           third pass (widths 1024, 2048) follows a team barrier.
+//                           third pass (widths 1024, 2048) follows a team barrier.  The warp
+//                           that finishes a batch last refills its slot with the batch S
+//                           further on, so copies run S - 1 batches ahead of their use.
+//
+// Inside every phase all shared-memory loads come first and all stores last (the compiler
+// cannot prove that the regions differ and would otherwise wait for each load before the next
+// store), and shared memory is addressed with 32-bit addresses throughout.
 //
 // Quantising replaces the dependent 2^bits-way boundary search by ONE table step: the value
 // is mapped linearly onto C cells (a fused multiply-add whose result's low mantissa bits are
@@ -38,11 +46,12 @@ __device__ int g_prologue_status = 0;  // 0 = ok; otherwise the code of the firs
 namespace {
 
 constexpr int kPwWarps = 8;                       // transform warps
-constexpr int kPwThreads = (kPwWarps + 1) * 32;   // + the norm warp
-constexpr int kPwNormWarp = kPwWarps;
+constexpr int kPwNormWarps = 2;
+constexpr int kPwThreads = (kPwWarps + kPwNormWarps) * 32;
 constexpr int kPwChunk = 1024;
 constexpr int kPwRowPad = 32;                     // bytes between the rows of a slot
 constexpr int kPwMaxRows = 4;                     // tokens per batch
+constexpr int kPwMaxSlots = 4;
 constexpr uint32_t kPwSpinLimit = 1u << 22;
 
 __host__ __device__ constexpr int pw_max_cells(int bits) {
@@ -61,6 +70,7 @@ struct WarpPrologueParams {
   int dim;
   int log2_block;
   int batch_rows;
+  int slots;
   float eps;
   float inv_sqrt_block;
   const float *w_centroids;
@@ -76,22 +86,22 @@ struct PwLayout {
   int row_pitch, slot_bytes, team_bytes, total;
 };
 
-__host__ __device__ inline PwLayout pw_layout(int dim, int block, int batch_rows, int bits) {
+__host__ __device__ inline PwLayout pw_layout(int dim, int block, int batch_rows, int slots, int bits) {
   PwLayout l;
   const int cells = pw_max_cells(bits);
-  int at = 128;  // barriers and flags
+  int at = 128;  // barriers, counters and flags
   l.cent = at;       at += 256 * 4;
   l.bnd = at;        at += 256 * 4;
   l.cell_bnd = at;   at += cells * 4;
   l.cell_meta = at;  at += (cells * 2 + 127) / 128 * 128;
-  l.slot_meta = at;  at += 2 * kPwMaxRows * 16;                       // norm, inv, opscale, -
-  l.outtab = at;     at += (2 * batch_rows * (2 << bits) + 127) / 128 * 128;
-  l.pairs = at;      at += 2 * batch_rows * cells * 4;
+  l.slot_meta = at;  at += kPwMaxSlots * kPwMaxRows * 16;             // norm, inv, opscale, -
+  l.outtab = at;     at += (slots * batch_rows * (2 << bits) + 127) / 128 * 128;
+  l.pairs = at;      at += slots * batch_rows * cells * 4;
   at = (at + 127) / 128 * 128;
   l.perm = at;       at += (dim + kPwChunk - 1) / kPwChunk * kPwChunk * 4;   // whole chunks
   l.row_pitch = dim * 2 + kPwRowPad;
   l.slot_bytes = batch_rows * l.row_pitch;
-  l.slots = at;      at += 2 * l.slot_bytes;
+  l.slots = at;      at += slots * l.slot_bytes;
   at = (at + 127) / 128 * 128;
   const int team = block > kPwChunk ? block / kPwChunk : 1;
   l.team_bytes = team * kPwChunk * 6;                                  // fp32 scratch + 16-bit results
@@ -102,6 +112,37 @@ __host__ __device__ inline PwLayout pw_layout(int dim, int block, int batch_rows
 
 __device__ __forceinline__ uint32_t pw_smem_u32(const void *p) {
   return static_cast<uint32_t>(__cvta_generic_to_shared(p));
+}
+
+// ---- shared memory through 32-bit addresses ----
+__device__ __forceinline__ uint32_t pw_lds_u16(uint32_t a) {
+  uint32_t v;   // a 32-bit destination: the loaded halfword arrives zero-extended
+  asm volatile("ld.shared.u16 %0, [%1];" : "=r"(v) : "r"(a));
+  return v;
+}
+__device__ __forceinline__ uint32_t pw_lds_u32(uint32_t a) {
+  uint32_t v;
+  asm volatile("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(a));
+  return v;
+}
+__device__ __forceinline__ float pw_lds_f32(uint32_t a) {
+  float v;
+  asm volatile("ld.shared.f32 %0, [%1];" : "=f"(v) : "r"(a));
+  return v;
+}
+__device__ __forceinline__ uint4 pw_lds_v4(uint32_t a) {
+  uint4 v;
+  asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(a));
+  return v;
+}
+__device__ __forceinline__ void pw_sts_v4f(uint32_t a, float x, float y, float z, float w) {
+  asm volatile("st.shared.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(a), "f"(x), "f"(y), "f"(z), "f"(w) : "memory");
+}
+__device__ __forceinline__ void pw_sts_f32(uint32_t a, float v) {
+  asm volatile("st.shared.f32 [%0], %1;" ::"r"(a), "f"(v) : "memory");
+}
+__device__ __forceinline__ void pw_sts_u16(uint32_t a, uint32_t v) {
+  asm volatile("st.shared.u16 [%0], %1;" ::"r"(a), "r"(v) : "memory");   // low halfword of v
 }
 
 __device__ __forceinline__ void pw_mbar_init(uint32_t bar, uint32_t count) {
@@ -207,50 +248,148 @@ __device__ __forceinline__ float pw_key_float(uint32_t k) {
   return __uint_as_float((k & 0x80000000u) ? (k & 0x7fffffffu) : ~k);
 }
 
-template <int S>
-__device__ __forceinline__ void pw_butterflies(float (&v)[S], int limit) {
+// Butterfly widths 1, 2, ... 2^(STAGES-1) over S register values.
+template <int S, int STAGES>
+__device__ __forceinline__ void pw_butterflies(float (&v)[S]) {
 #pragma unroll
-  for (int h = 1; h < S; h <<= 1) {
-    if (h < limit) {
+  for (int stage = 0; stage < STAGES; ++stage) {
+    const int h = 1 << stage;
 #pragma unroll
-      for (int a = 0; a < S; ++a) {
-        if ((a & h) == 0) {
-          const float l = v[a];
-          const float r = v[a | h];
-          v[a] = __fadd_rn(l, r);
-          v[a | h] = __fsub_rn(l, r);
-        }
+    for (int a = 0; a < S; ++a) {
+      if ((a & h) == 0) {
+        const float l = v[a];
+        const float r = v[a | h];
+        v[a] = __fadd_rn(l, r);
+        v[a | h] = __fsub_rn(l, r);
       }
     }
   }
 }
 
-// State a transform thread needs to quantise values of one token.
+// What a transform thread needs to quantise values of one token.
 struct PwQuant {
   PwCellMap map;
-  const unsigned char *cell_bnd;   // float per cell
-  const unsigned char *pairs;      // this token's candidate pair per cell
-  const float *bnd;                // boundaries (fallback search)
-  const uint16_t *outtab;          // this token's 2^bits outputs (fallback search)
+  // shared addresses of the per-cell boundaries (float) and of this token's candidate pairs,
+  // both minus 4 * 0x4B000000: the cell number arrives as 2^23 + cell in a float's bits
+  uint32_t cell_bnd;
+  uint32_t pairs;
+  const float *bnd;    // boundaries (fallback search)
+  const uint16_t *outtab;  // this token's 2^bits outputs (fallback search)
   float isb;
-  bool use_cells;
 };
 
-template <int BITS>
-__device__ __forceinline__ uint16_t pw_quantize(float value, const PwQuant &q) {
-  const float d = __fmul_rn(value, q.isb);
-  if (q.use_cells) {
-    const uint32_t off = (pw_cell_bits(d, q.map) << 2) - 0x2C000000u;  // 4 * (bits - 0x4B000000)
-    const float b = *reinterpret_cast<const float *>(q.cell_bnd + off);
-    const uint32_t pair = *reinterpret_cast<const uint32_t *>(q.pairs + off);
-    return static_cast<uint16_t>(!(d <= b) ? (pair >> 16) : pair);
-  }
-  int pos = 0;
+// Quantises N register values in place (the results replace the values as raw 16-bit patterns).
+template <int BITS, bool CELLS, int N>
+__device__ __forceinline__ void pw_quantize_all(float (&w)[N], const PwQuant &q) {
+  if (CELLS) {
+    // groups of up to 8: the table reads of a group are in flight together, and the register
+    // budget stays within two CTAs per SM
+    constexpr int kGroup = N < 8 ? N : 8;
 #pragma unroll
-  for (int step = 1 << (BITS - 1); step >= 1; step >>= 1) {
-    pos += !(d <= q.bnd[pos + step - 1]) ? step : 0;
+    for (int a0 = 0; a0 < N; a0 += kGroup) {
+      float d[kGroup];
+      float b[kGroup];
+      uint32_t pair[kGroup];
+#pragma unroll
+      for (int a = 0; a < kGroup; ++a) {
+        d[a] = __fmul_rn(w[a0 + a], q.isb);
+        const uint32_t off = pw_cell_bits(d[a], q.map) << 2;
+        b[a] = pw_lds_f32(q.cell_bnd + off);
+        pair[a] = pw_lds_u32(q.pairs + off);
+      }
+#pragma unroll
+      for (int a = 0; a < kGroup; ++a) {
+        w[a0 + a] = __uint_as_float(!(d[a] <= b[a]) ? (pair[a] >> 16) : pair[a]);
+      }
+    }
+  } else {
+#pragma unroll
+    for (int a = 0; a < N; ++a) {
+      const float d = __fmul_rn(w[a], q.isb);
+      int pos = 0;
+#pragma unroll
+      for (int step = 1 << (BITS - 1); step >= 1; step >>= 1) {
+        pos += !(d <= q.bnd[pos + step - 1]) ? step : 0;
+      }
+      w[a] = __uint_as_float(static_cast<uint32_t>(q.outtab[pos]));
+    }
   }
-  return q.outtab[pos];
+}
+
+// Pass B of one chunk (and, for blocks up to 1024, the quantisation): lane b owns column b of
+// the 32 x 32 arrangement held in the warp's scratch.
+template <int BITS, bool CELLS, int STAGES, bool FINAL>
+__device__ __forceinline__ void pw_pass_b(uint32_t scratch, uint32_t result, int lane, int active_rows,
+                                          const PwQuant &q) {
+  float w[32];
+  const uint32_t column = scratch + ((lane & 3) << 2);
+  const uint32_t group = static_cast<uint32_t>(lane >> 2);
+#pragma unroll
+  for (int a = 0; a < 32; ++a) {
+    w[a] = pw_lds_f32(column + a * 128 + ((group ^ (a & 7)) << 4));
+  }
+  pw_butterflies<32, STAGES>(w);
+  if (FINAL) {
+    pw_quantize_all<BITS, CELLS, 32>(w, q);
+    if (lane == 0) {
+      pw_bulk_store_wait_read();   // the previous chunk's results have left the staging area
+    }
+    __syncwarp();
+    const uint32_t dst = result + lane * 2;
+    if (active_rows == 32) {
+#pragma unroll
+      for (int a = 0; a < 32; ++a) {
+        pw_sts_u16(dst + a * 64, __float_as_uint(w[a]));
+      }
+    } else {
+#pragma unroll
+      for (int a = 0; a < 32; ++a) {
+        if (a < active_rows) {
+          pw_sts_u16(dst + a * 64, __float_as_uint(w[a]));
+        }
+      }
+    }
+  } else {
+    __syncwarp();   // every lane has read its column before the scratch is rewritten
+    const uint32_t dst = scratch + lane * 4;
+#pragma unroll
+    for (int a = 0; a < 32; ++a) {
+      pw_sts_f32(dst + a * 128, w[a]);
+    }
+  }
+}
+
+// Pass C of a team block: widths 1024 (and 2048) across the team's TEAM chunks, then the
+// quantisation.  Thread tt of the team owns positions tt, tt + threads, ...
+template <int BITS, bool CELLS, int TEAM>
+__device__ __forceinline__ void pw_pass_c(uint32_t scratch, uint32_t result, int tt, const PwQuant &q) {
+  constexpr int kThreads = TEAM * 32;
+  constexpr int kPer = kPwChunk / kThreads;   // positions per thread: 16 (two chunks) or 8 (four)
+  constexpr int kBatch = 8 / TEAM;            // positions handled together: TEAM * kBatch = 8 values
+  constexpr int kStages = TEAM == 2 ? 1 : 2;
+#pragma unroll 1
+  for (int i0 = 0; i0 < kPer; i0 += kBatch) {
+    float c[kBatch][TEAM];
+#pragma unroll
+    for (int i = 0; i < kBatch; ++i) {
+#pragma unroll
+      for (int t = 0; t < TEAM; ++t) {
+        c[i][t] = pw_lds_f32(scratch + (t * kPwChunk + tt + kThreads * (i0 + i)) * 4);
+      }
+    }
+#pragma unroll
+    for (int i = 0; i < kBatch; ++i) {
+      pw_butterflies<TEAM, kStages>(c[i]);
+      pw_quantize_all<BITS, CELLS, TEAM>(c[i], q);
+    }
+#pragma unroll
+    for (int i = 0; i < kBatch; ++i) {
+#pragma unroll
+      for (int t = 0; t < TEAM; ++t) {
+        pw_sts_u16(result + (t * kPwChunk + tt + kThreads * (i0 + i)) * 2, __float_as_uint(c[i][t]));
+      }
+    }
+  }
 }
 
 template <int BITS, bool F16OP>
@@ -261,31 +400,30 @@ rotate_quantize_warp_kernel(const WarpPrologueParams p) {
   constexpr int kMaxCells = pw_max_cells(BITS);
   const uint32_t raw_addr = pw_smem_u32(pw_smem_raw);
   unsigned char *smem = pw_smem_raw + (((raw_addr + 127u) & ~127u) - raw_addr);
+  const uint32_t smem_addr = pw_smem_u32(smem);
   const int dim = p.dim;
   const int block = 1 << p.log2_block;
   const int R = p.batch_rows;
-  const PwLayout lay = pw_layout(dim, block, R, BITS);
+  const int S = p.slots;
+  const PwLayout lay = pw_layout(dim, block, R, S, BITS);
 
-  uint64_t *bars = reinterpret_cast<uint64_t *>(smem);
-  volatile int *s_fallback = reinterpret_cast<volatile int *>(smem + 64);
-  volatile int *s_abort = reinterpret_cast<volatile int *>(smem + 68);
-  volatile int *s_cells = reinterpret_cast<volatile int *>(smem + 72);
+  // bytes 0..63: full[4] normed[4] barriers; 64..79: done counters; 80..: flags
+  int *s_done = reinterpret_cast<int *>(smem + 64);
+  volatile int *s_fallback = reinterpret_cast<volatile int *>(smem + 80);
+  volatile int *s_abort = reinterpret_cast<volatile int *>(smem + 84);
+  volatile int *s_cells = reinterpret_cast<volatile int *>(smem + 88);
   float *s_cent = reinterpret_cast<float *>(smem + lay.cent);
   float *s_bnd = reinterpret_cast<float *>(smem + lay.bnd);
   float *s_cell_bnd = reinterpret_cast<float *>(smem + lay.cell_bnd);
   uint16_t *s_cell_meta = reinterpret_cast<uint16_t *>(smem + lay.cell_meta);
-  float *s_slot_meta = reinterpret_cast<float *>(smem + lay.slot_meta);   // [2][R]{norm, inv, opscale, -}
-  uint16_t *s_outtab = reinterpret_cast<uint16_t *>(smem + lay.outtab);   // [2][R][levels]
-  uint32_t *s_pairs = reinterpret_cast<uint32_t *>(smem + lay.pairs);     // [2][R][max cells]
+  float *s_slot_meta = reinterpret_cast<float *>(smem + lay.slot_meta);   // [S][4]{norm, inv, opscale, -}
+  uint16_t *s_outtab = reinterpret_cast<uint16_t *>(smem + lay.outtab);   // [S][R][levels]
+  uint32_t *s_pairs = reinterpret_cast<uint32_t *>(smem + lay.pairs);     // [S][R][max cells]
   uint32_t *s_perm = reinterpret_cast<uint32_t *>(smem + lay.perm);
-  unsigned char *s_slots = smem + lay.slots;
-  unsigned char *s_work = smem + lay.work;
-  float *s_dmin = reinterpret_cast<float *>(s_work);                       // set-up only
+  float *s_dmin = reinterpret_cast<float *>(smem + lay.work);             // set-up only
 
-  const uint32_t bar_base = pw_smem_u32(bars);
-  auto full_bar = [&](int s) { return bar_base + 8u * s; };
-  auto normed_bar = [&](int s) { return bar_base + 16u + 8u * s; };
-  auto empty_bar = [&](int s) { return bar_base + 32u + 8u * s; };
+  auto full_bar = [&](int s) { return smem_addr + 8u * s; };
+  auto normed_bar = [&](int s) { return smem_addr + 32u + 8u * s; };
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -304,16 +442,33 @@ rotate_quantize_warp_kernel(const WarpPrologueParams p) {
     return;
   }
 
-  // ---- set-up: barriers, codebook, permutation table, cell table ----
+  const int64_t n_batches = (p.rows + R - 1) / R;
+  // CTA-local batch b is global batch blockIdx.x + b * workers
+  const int my_batches = static_cast<int>((n_batches - blockIdx.x + workers - 1) / workers);
+  auto issue_load = [&](int local_batch) {   // one thread
+    const int slot = local_batch % S;
+    const int64_t row0 = (static_cast<int64_t>(blockIdx.x) + static_cast<int64_t>(local_batch) * workers) * R;
+    const int nrows = static_cast<int>(min(static_cast<int64_t>(R), p.rows - row0));
+    pw_mbar_expect_tx(full_bar(slot), static_cast<uint32_t>(nrows) * dim * 2);
+    for (int rr = 0; rr < nrows; ++rr) {
+      pw_bulk_load(smem_addr + lay.slots + slot * lay.slot_bytes + rr * lay.row_pitch,
+                   p.x + (row0 + rr) * dim, static_cast<uint32_t>(dim) * 2, full_bar(slot));
+    }
+  };
+
+  // ---- set-up: barriers and the first copies, codebook, permutation table, cell table ----
   if (threadIdx.x == 0) {
-    for (int s = 0; s < 2; ++s) {
+    for (int s = 0; s < kPwMaxSlots; ++s) {
       pw_mbar_init(full_bar(s), 1);
       pw_mbar_init(normed_bar(s), 1);
-      pw_mbar_init(empty_bar(s), kPwWarps);
+      s_done[s] = 0;
     }
     *s_fallback = 0;
     *s_abort = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    for (int b = 0; b < S && b < my_batches; ++b) {
+      issue_load(b);
+    }
   }
   for (int i = threadIdx.x; i < kLevels; i += kPwThreads) {
     s_cent[i] = p.centroids[i];
@@ -322,11 +477,41 @@ rotate_quantize_warp_kernel(const WarpPrologueParams p) {
   // entry of rotated position i: byte offset of its source element in the row | sign << 31.
   // Stored so that lane l's 16-byte read of group g of a chunk is conflict-free:
   // [chunk][g = (i % 32) / 4][lane = (i % 1024) / 32][i % 4].
-  for (int i = threadIdx.x; i < dim; i += kPwThreads) {
-    const uint32_t entry = (static_cast<uint32_t>(p.perm[i]) << 1) | (p.signs[i] < 0 ? 0x80000000u : 0u);
-    const int within = i & (kPwChunk - 1);
-    const int slot_index = (i - within) + ((within & 31) >> 2) * 128 + (within >> 5) * 4 + (within & 3);
-    s_perm[slot_index] = entry;
+  // Four positions per 16-byte read, four reads in flight per thread before any is used (the
+  // table build is pure global-memory latency otherwise).
+  {
+    const int groups = dim >> 2;
+    const int4 *perm4 = reinterpret_cast<const int4 *>(p.perm);
+    const uint32_t *signs4 = reinterpret_cast<const uint32_t *>(p.signs);
+    for (int g0 = threadIdx.x; g0 < groups; g0 += 4 * kPwThreads) {
+      int4 pv[4];
+      uint32_t sv[4];
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const int g = g0 + u * kPwThreads;
+        if (g < groups) {
+          pv[u] = __ldg(perm4 + g);
+          sv[u] = __ldg(signs4 + g);
+        }
+      }
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const int g = g0 + u * kPwThreads;
+        if (g < groups) {
+          const int i = g << 2;   // positions i .. i + 3 share a lane and a 16-byte group
+          const int within = i & (kPwChunk - 1);
+          const int slot_index = (i - within) + ((within & 31) >> 2) * 128 + (within >> 5) * 4;
+          const int src[4] = {pv[u].x, pv[u].y, pv[u].z, pv[u].w};
+          uint4 entry;
+          uint32_t *e = reinterpret_cast<uint32_t *>(&entry);
+#pragma unroll
+          for (int q = 0; q < 4; ++q) {
+            e[q] = (static_cast<uint32_t>(src[q]) << 1) | ((sv[u] << (24 - 8 * q)) & 0x80000000u);
+          }
+          *reinterpret_cast<uint4 *>(s_perm + slot_index) = entry;
+        }
+      }
+    }
   }
   __syncthreads();
 
@@ -351,6 +536,17 @@ rotate_quantize_warp_kernel(const WarpPrologueParams p) {
         } else {
           uint32_t below = pw_float_key(lo);           // cell(below) < c
           uint32_t reach = pw_float_key(hi);           // cell(reach) >= c
+          // start from the inverse of the map where a narrow bracket around it holds
+          const float guess = __fmaf_rn(__fdiv_rn(static_cast<float>(c) - 1.5f, map.scale), 1.0f, lo);
+          const uint32_t centre = pw_float_key(fmaxf(fminf(guess, hi), lo));
+          const uint32_t near_lo = centre - below > 256u ? centre - 256u : below;
+          const uint32_t near_hi = reach - centre > 256u ? centre + 256u : reach;
+          if (pw_cell_bits(pw_key_float(near_lo), map) - 0x4B000000u < static_cast<uint32_t>(c)) {
+            below = near_lo;
+          }
+          if (pw_cell_bits(pw_key_float(near_hi), map) - 0x4B000000u >= static_cast<uint32_t>(c)) {
+            reach = near_hi;
+          }
           while (reach - below > 1u) {
             const uint32_t mid = below + ((reach - below) >> 1);
             const uint32_t cell = pw_cell_bits(pw_key_float(mid), map) - 0x4B000000u;
@@ -395,31 +591,17 @@ rotate_quantize_warp_kernel(const WarpPrologueParams p) {
     cells = *s_cells;
   }
   const PwCellMap map = pw_cell_map(lo, hi, use_cells ? cells : 8);
-
   const int units_per_row = block > kPwChunk ? dim / block : (dim + kPwChunk - 1) / kPwChunk;
-  const int64_t n_batches = (p.rows + R - 1) / R;
 
-  if (warp == kPwNormWarp) {
-    // ================= norm warp =================
+  if (warp >= kPwWarps) {
+    // ================= norm warps: alternate batches =================
     const int r = lane >> 3;
     const int t = lane & 7;
-    int bi = 0;
-    for (int64_t batch = blockIdx.x; batch < n_batches; batch += workers, ++bi) {
-      const int slot = bi & 1;
-      const uint32_t use = static_cast<uint32_t>(bi >> 1);
-      const int64_t row0 = batch * R;
+    for (int bi = warp - kPwWarps; bi < my_batches; bi += kPwNormWarps) {
+      const int slot = bi % S;
+      const uint32_t use = static_cast<uint32_t>(bi / S);
+      const int64_t row0 = (static_cast<int64_t>(blockIdx.x) + static_cast<int64_t>(bi) * workers) * R;
       const int nrows = static_cast<int>(min(static_cast<int64_t>(R), p.rows - row0));
-      if (!pw_mbar_wait(empty_bar(slot), (use & 1u) ^ 1u, s_abort, 1)) {
-        break;
-      }
-      unsigned char *slot_ptr = s_slots + slot * lay.slot_bytes;
-      if (lane == 0) {
-        pw_mbar_expect_tx(full_bar(slot), static_cast<uint32_t>(nrows) * dim * 2);
-        for (int rr = 0; rr < nrows; ++rr) {
-          pw_bulk_load(pw_smem_u32(slot_ptr + rr * lay.row_pitch), p.x + (row0 + rr) * dim,
-                       static_cast<uint32_t>(dim) * 2, full_bar(slot));
-        }
-      }
       if (!pw_mbar_wait(full_bar(slot), use & 1u, s_abort, 2)) {
         break;
       }
@@ -427,14 +609,14 @@ rotate_quantize_warp_kernel(const WarpPrologueParams p) {
       float acc0 = 0.0f;
       float acc1 = 0.0f;
       if (r < nrows) {
-        const uint32_t *src = reinterpret_cast<const uint32_t *>(slot_ptr + r * lay.row_pitch) + t;
+        const uint32_t src = smem_addr + lay.slots + slot * lay.slot_bytes + r * lay.row_pitch + t * 4;
         const int iters = dim >> 4;
         int i = 0;
         for (; i + 8 <= iters; i += 8) {
           uint32_t w[8];
 #pragma unroll
           for (int u = 0; u < 8; ++u) {
-            w[u] = src[(i + u) * 8];
+            w[u] = pw_lds_u32(src + (i + u) * 32);
           }
 #pragma unroll
           for (int u = 0; u < 8; ++u) {
@@ -445,7 +627,7 @@ rotate_quantize_warp_kernel(const WarpPrologueParams p) {
           }
         }
         for (; i < iters; ++i) {
-          const uint32_t w = src[i * 8];
+          const uint32_t w = pw_lds_u32(src + i * 32);
           const float a = __uint_as_float(w << 16);
           const float b = __uint_as_float(w & 0xffff0000u);
           acc0 = __fmaf_rn(a, a, acc0);
@@ -516,146 +698,139 @@ rotate_quantize_warp_kernel(const WarpPrologueParams p) {
   const int tw = warp - team * team_size;
   const int team_threads = team_size * 32;
   const int tt = tw * 32 + lane;
-  float *scratch = reinterpret_cast<float *>(s_work + team * lay.team_bytes);          // [team][1024] fp32
-  uint16_t *result = reinterpret_cast<uint16_t *>(scratch + team_size * kPwChunk);     // [team][1024]
-  float *my_scratch = scratch + tw * kPwChunk;
-  const int passb_limit = block >= kPwChunk ? 32 : (block >> 5);  // butterfly widths of pass B, in rows of 32
+  const uint32_t scratch = smem_addr + lay.work + team * lay.team_bytes;        // [team][1024] fp32
+  const uint32_t result = scratch + team_size * kPwChunk * 4;                    // [team][1024] 16-bit
+  const uint32_t my_scratch = scratch + tw * kPwChunk * 4;
+  const uint32_t my_rows = my_scratch + lane * 128;
+  const uint32_t perm_base = smem_addr + lay.perm + lane * 16;
 
   PwQuant quant;
   quant.map = map;
-  quant.cell_bnd = reinterpret_cast<const unsigned char *>(s_cell_bnd);
+  quant.cell_bnd = smem_addr + lay.cell_bnd - 0x2C000000u;
   quant.bnd = s_bnd;
   quant.isb = p.inv_sqrt_block;
-  quant.use_cells = use_cells;
 
-  int bi = 0;
   int64_t unit_base = 0;   // units of this CTA before the current batch
-  bool ok = true;
-  for (int64_t batch = blockIdx.x; batch < n_batches && ok; batch += workers, ++bi) {
-    const int slot = bi & 1;
-    const uint32_t use = static_cast<uint32_t>(bi >> 1);
-    const int64_t row0 = batch * R;
+  for (int bi = 0; bi < my_batches; ++bi) {
+    const int slot = bi % S;
+    const uint32_t use = static_cast<uint32_t>(bi / S);
+    const int64_t row0 = (static_cast<int64_t>(blockIdx.x) + static_cast<int64_t>(bi) * workers) * R;
     const int nrows = static_cast<int>(min(static_cast<int64_t>(R), p.rows - row0));
     const int units = nrows * units_per_row;
     if (!pw_mbar_wait(normed_bar(slot), use & 1u, s_abort, 3)) {
-      ok = false;
       break;
     }
-    const unsigned char *slot_ptr = s_slots + slot * lay.slot_bytes;
-    int first = static_cast<int>((team - unit_base % n_teams + n_teams) % n_teams);
+    const uint32_t slot_addr = smem_addr + lay.slots + slot * lay.slot_bytes;
+    const int first = static_cast<int>((team - unit_base % n_teams + n_teams) % n_teams);
     for (int j = first; j < units; j += n_teams) {
       const int r = j / units_per_row;
       const int u = j - r * units_per_row;
       const float inv = s_slot_meta[(slot * kPwMaxRows + r) * 4 + 1];
-      quant.pairs = reinterpret_cast<const unsigned char *>(s_pairs + (slot * R + r) * kMaxCells);
+      quant.pairs = smem_addr + lay.pairs + ((slot * R + r) * kMaxCells) * 4 - 0x2C000000u;
       quant.outtab = s_outtab + (slot * R + r) * kLevels;
-      const unsigned char *row_ptr = slot_ptr + r * lay.row_pitch;
+      const uint32_t row_addr = slot_addr + r * lay.row_pitch;
       // this warp's 1024-element chunk: positions chunk_first .. chunk_first + chunk_len
       const int chunk_index = team_size > 1 ? u * team_size + tw : u;
       const int chunk_first = chunk_index * kPwChunk;
       const int chunk_len = min(kPwChunk, dim - chunk_first);
       const int active_lanes = chunk_len >> 5;
 
-      // ---- pass A: gather, widths 1 .. 16 ----
-      float v[32];
-      if (lane < active_lanes) {
-        const uint4 *entries = reinterpret_cast<const uint4 *>(s_perm + chunk_first) + lane;
+      // ---- pass A: gather, widths 1 .. 16, transposing store ----
+      {
+        float v[32];
+        if (lane < active_lanes) {
+          const uint32_t entries = perm_base + chunk_first * 4;
+          uint32_t e[32];
 #pragma unroll
-        for (int g = 0; g < 8; ++g) {
-          const uint4 e4 = entries[g * 32];
-          const uint32_t e[4] = {e4.x, e4.y, e4.z, e4.w};
+          for (int g = 0; g < 8; ++g) {
+            const uint4 e4 = pw_lds_v4(entries + g * 512);
+            e[4 * g] = e4.x;
+            e[4 * g + 1] = e4.y;
+            e[4 * g + 2] = e4.z;
+            e[4 * g + 3] = e4.w;
+          }
+          uint32_t raw[32];
 #pragma unroll
-          for (int q = 0; q < 4; ++q) {
-            const uint32_t raw = *reinterpret_cast<const uint16_t *>(row_ptr + (e[q] & 0xffffu));
-            v[4 * g + q] = __fmul_rn(__uint_as_float((raw << 16) ^ (e[q] & 0x80000000u)), inv);
+          for (int q = 0; q < 32; ++q) {
+            raw[q] = pw_lds_u16(row_addr + (e[q] & 0xffffu));
+          }
+#pragma unroll
+          for (int q = 0; q < 32; ++q) {
+            v[q] = __fmul_rn(__uint_as_float((raw[q] << 16) ^ (e[q] & 0x80000000u)), inv);
+          }
+        } else {
+#pragma unroll
+          for (int q = 0; q < 32; ++q) {
+            v[q] = 0.0f;
           }
         }
-      } else {
-#pragma unroll
-        for (int q = 0; q < 32; ++q) {
-          v[q] = 0.0f;
-        }
-      }
-      pw_butterflies<32>(v, 32);
-      // transpose through the scratch: 16-byte group g of lane l goes to slot g ^ (l & 7)
-      {
-        float4 *dst = reinterpret_cast<float4 *>(my_scratch + lane * 32);
+        pw_butterflies<32, 5>(v);
+        // 16-byte group g of lane l goes to slot g ^ (l & 7) of the lane's 128-byte row
+        const uint32_t swz = static_cast<uint32_t>(lane & 7);
 #pragma unroll
         for (int g = 0; g < 8; ++g) {
-          dst[g ^ (lane & 7)] = make_float4(v[4 * g], v[4 * g + 1], v[4 * g + 2], v[4 * g + 3]);
+          pw_sts_v4f(my_rows + ((g ^ swz) << 4), v[4 * g], v[4 * g + 1], v[4 * g + 2], v[4 * g + 3]);
         }
       }
       __syncwarp();
-      // ---- pass B: lane b owns column b of the 32 x 32 arrangement, widths 32 .. 512 ----
-      float w[32];
-#pragma unroll
-      for (int a = 0; a < 32; ++a) {
-        w[a] = my_scratch[a * 32 + ((((lane >> 2) ^ (a & 7)) << 2) | (lane & 3))];
-      }
-      pw_butterflies<32>(w, passb_limit);
       if (team_size == 1) {
-        if (lane == 0) {
-          pw_bulk_store_wait_read();   // the previous chunk's results have left the staging area
-        }
-        __syncwarp();
-#pragma unroll
-        for (int a = 0; a < 32; ++a) {
-          if (a < active_lanes) {
-            result[a * 32 + lane] = pw_quantize<BITS>(w[a], quant);
+        // ---- pass B with the quantisation; widths up to the block ----
+        if (use_cells) {
+          switch (p.log2_block) {
+            case 8: pw_pass_b<BITS, true, 3, true>(my_scratch, result, lane, active_lanes, quant); break;
+            case 9: pw_pass_b<BITS, true, 4, true>(my_scratch, result, lane, active_lanes, quant); break;
+            default: pw_pass_b<BITS, true, 5, true>(my_scratch, result, lane, active_lanes, quant); break;
+          }
+        } else {
+          switch (p.log2_block) {
+            case 8: pw_pass_b<BITS, false, 3, true>(my_scratch, result, lane, active_lanes, quant); break;
+            case 9: pw_pass_b<BITS, false, 4, true>(my_scratch, result, lane, active_lanes, quant); break;
+            default: pw_pass_b<BITS, false, 5, true>(my_scratch, result, lane, active_lanes, quant); break;
           }
         }
         pw_fence_async();
         __syncwarp();
         if (lane == 0) {
-          pw_bulk_store(p.xq + (row0 + r) * dim + chunk_first, pw_smem_u32(result),
-                        static_cast<uint32_t>(chunk_len) * 2);
+          pw_bulk_store(p.xq + (row0 + r) * dim + chunk_first, result, static_cast<uint32_t>(chunk_len) * 2);
         }
       } else {
-        // ---- pass C: widths 1024 (and 2048) across the team's chunks ----
-        __syncwarp();   // every lane has read its column before the scratch is rewritten
-#pragma unroll
-        for (int a = 0; a < 32; ++a) {
-          my_scratch[a * 32 + lane] = w[a];
-        }
+        // ---- pass B (widths 32 .. 512) back into the scratch, then pass C across the team ----
+        pw_pass_b<BITS, true, 5, false>(my_scratch, result, lane, 32, quant);
         if (tt == 0) {
           pw_bulk_store_wait_read();
         }
         pw_team_barrier(team, team_threads);
-        const int per_thread = kPwChunk / team_threads;   // 16 (two chunks) or 8 (four)
-        if (team_size == 2) {
-#pragma unroll 4
-          for (int i = 0; i < per_thread; ++i) {
-            const int pos = tt + team_threads * i;
-            float c[2] = {scratch[pos], scratch[kPwChunk + pos]};
-            pw_butterflies<2>(c, 2);
-            result[pos] = pw_quantize<BITS>(c[0], quant);
-            result[kPwChunk + pos] = pw_quantize<BITS>(c[1], quant);
+        if (use_cells) {
+          if (team_size == 2) {
+            pw_pass_c<BITS, true, 2>(scratch, result, tt, quant);
+          } else {
+            pw_pass_c<BITS, true, 4>(scratch, result, tt, quant);
           }
+        } else if (team_size == 2) {
+          pw_pass_c<BITS, false, 2>(scratch, result, tt, quant);
         } else {
-#pragma unroll 4
-          for (int i = 0; i < per_thread; ++i) {
-            const int pos = tt + team_threads * i;
-            float c[4] = {scratch[pos], scratch[kPwChunk + pos], scratch[2 * kPwChunk + pos],
-                          scratch[3 * kPwChunk + pos]};
-            pw_butterflies<4>(c, 4);
-#pragma unroll
-            for (int q = 0; q < 4; ++q) {
-              result[q * kPwChunk + pos] = pw_quantize<BITS>(c[q], quant);
-            }
-          }
+          pw_pass_c<BITS, false, 4>(scratch, result, tt, quant);
         }
         pw_fence_async();
         pw_team_barrier(team, team_threads);   // results complete; scratch free for the next unit
         if (tt == 0) {
-          pw_bulk_store(p.xq + (row0 + r) * dim + static_cast<int64_t>(u) * block, pw_smem_u32(result),
+          pw_bulk_store(p.xq + (row0 + r) * dim + static_cast<int64_t>(u) * block, result,
                         static_cast<uint32_t>(block) * 2);
         }
       }
     }
     unit_base += units;
+    // The warp that finishes the batch last refills the slot with the batch S further on.
     __syncwarp();
     if (lane == 0) {
-      pw_mbar_arrive(empty_bar(slot));
+      __threadfence_block();
+      if (atomicAdd(&s_done[slot], 1) == kPwWarps - 1) {
+        atomicExch(&s_done[slot], 0);
+        if (bi + S < my_batches) {
+          pw_fence_async();
+          issue_load(bi + S);
+        }
+      }
     }
   }
   if (lane == 0) {
