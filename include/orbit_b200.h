@@ -126,6 +126,31 @@ int oq_quantize_activations(const void *x, int x_dtype, int64_t rows, int64_t di
                             const float *boundaries, const float *centroids, int bits,
                             float eps, void *x_q, uint8_t *codes, float *norms, void *stream);
 
+/* The same pipeline with the output forms the reference's integer matmul consumes
+ * (op schemas torch-ext/torch_binding.cpp:32-62):
+ *
+ * oq_quantize_activations_packed_w4: 4-bit activation indices packed two per byte (low
+ * nibble = even k) into packed_out[rows, dim/2] plus the token norms f32[rows].  Replaces
+ * quantize_activations_packed_w4 (orbitquant_packed_matmul_cuda/packed_matmul.cu:581-657,
+ * host :1894-2023; src/orbitquant/kernels/triton_cuda.py:290-357); any block dividing dim is
+ * accepted, not only block == dim.  The indices are the ones of oq_quantize_activations
+ * (reference CPU AVX-512 order).  The workspace holds the unpacked indices.
+ *
+ * oq_quantize_activations_int8: codes_out[rows, dim] = act_codes[index] (int8) plus the
+ * token norms -- the INT8 surrogate activation stream.  Replaces quantize_activations_int8
+ * (packed_matmul.cu:659-742, host :2025-2164). */
+size_t oq_quantize_activations_packed_w4_workspace_bytes(int64_t rows, int64_t dim);
+int oq_quantize_activations_packed_w4(const void *x, int x_dtype, int64_t rows, int64_t dim,
+                                      const int32_t *perm, const int8_t *signs, int64_t block,
+                                      const float *boundaries, const float *centroids, float eps,
+                                      uint8_t *packed_out, float *norms_out, void *workspace,
+                                      size_t workspace_bytes, void *stream);
+int oq_quantize_activations_int8(const void *x, int x_dtype, int64_t rows, int64_t dim,
+                                 const int32_t *perm, const int8_t *signs, int64_t block,
+                                 const float *boundaries, const float *centroids, int bits,
+                                 const int8_t *act_codes, float eps, int8_t *codes_out,
+                                 float *norms_out, void *stream);
+
 /* ---- packed-weight matmul ----------------------------------------------------------- */
 
 /* out[m,n] = sum_k x[m,k] * W[n,k] (+ bias[n]),  W decoded on the fly from the packed
@@ -176,6 +201,44 @@ int oq_gemm_tcgen05_f16(void *out, const void *x_f16, const float *row_scale,
 int oq_rows_to_f16_operand(const void *x, int dtype, int64_t rows, int64_t dim, void *x_f16,
                            float *row_scale, const float *centroids, int bits,
                            float *table_scale, void *stream);
+
+/* ---- integer-index formulations --------------------------------------------------- */
+
+/* INT8-surrogate matmul: out[m, n] = (sum_k act_codes[a[m,k]] * weight_codes[w[n,k]])
+ *   * token_norms[m] * row_norm[n] * act_scale * weight_scale + bias[n], bf16 output.
+ * packed_act is the nibble stream of oq_quantize_activations_packed_w4; the weights are the
+ * ordinary packed stream (2, 3, 4 or 6 bits); the code tables and scales come from the
+ * reference's fit_int8_centroid_surrogate (src/orbitquant/kernels/triton_cuda.py:1826-1857).
+ * Replaces matmul_packed_w4a4_int8 (packed_matmul.cu:744-1009, host :1715-1892) and the
+ * fused Triton kernels (triton_cuda.py:1861-2099).  Approximate by construction (the codes
+ * are rounded centroids); the integer contraction itself is exact: it runs on the f16 tensor
+ * cores, where INT8 codes, their products and sums below 2^24 are exact.
+ * Three launches (code table, operand expansion, GEMM); in_features % 64 == 0. */
+size_t oq_matmul_packed_w4a4_int8_workspace_bytes(int64_t rows, int64_t in_features);
+int oq_matmul_packed_w4a4_int8(void *out, const uint8_t *packed_act, const uint8_t *packed_weight,
+                               int64_t packed_weight_bytes, int weight_bits, const float *token_norms,
+                               const void *row_norms_bf16, const int8_t *act_codes,
+                               const int8_t *weight_codes, const void *bias, int bias_dtype,
+                               float act_scale, float weight_scale, int64_t rows, int64_t in_features,
+                               int64_t out_features, void *workspace, size_t workspace_bytes,
+                               void *stream);
+
+/* Exact W4A4 linear through the 256-entry pair-product table:
+ *   out[m, n] = (sum_k pair_lut[16 * a[m,k] + w[n,k]]) * token_norm[m] * row_norm[n] + bias[n]
+ * in fp32, rounded to x's dtype, pair_lut[16 i + j] = act_centroid[i] * weight_centroid[j].
+ * Replaces orbitquant_vulkan::linear_w4a4_exact, i.e. the arithmetic of
+ * _linear_w4a4_exact_reference (src/orbitquant/kernels/executorch_vulkan.py:15-61; the shader
+ * native-kernels/orbitquant-vulkan/glsl/orbitquant_w4a4_lut_tiled.glsl computes the same).
+ * The table entries are added in ascending k by one thread per output element; the
+ * activation indices are those of oq_quantize_activations. */
+size_t oq_linear_w4a4_pair_lut_workspace_bytes(int64_t rows, int64_t in_features);
+int oq_linear_w4a4_pair_lut(void *out, const void *x, int dtype, int64_t rows, int64_t in_features,
+                            int64_t out_features, const uint8_t *packed, int64_t packed_bytes,
+                            const void *row_norms_bf16, const void *bias, int bias_dtype,
+                            const int32_t *perm, const int8_t *signs, int64_t block,
+                            const float *act_boundaries, const float *act_centroids,
+                            const float *pair_lut, float eps, void *workspace, size_t workspace_bytes,
+                            void *stream);
 
 /* ---- the whole quantized-linear forward --------------------------------------------- */
 

@@ -166,3 +166,57 @@ def rtn_int4_matmul(x, packed, scales, *, out_features, in_features, group_size=
         acc += bias.cpu().to(torch.float32).numpy()[None, :]
     out = torch.from_numpy(acc).to(torch.bfloat16)
     return out.reshape(*x.shape[:-1], out_features)
+
+
+def pair_lut_linear(x, packed, row_norms, bias, *, perm, signs, block, act_boundaries, act_centroids,
+                    pair_lut, out_features, eps=1e-10, norm_order=NORM_AVX512):
+    """Exact W4A4 linear through the 256-entry pair-product table, the arithmetic of the
+    reference's ``_linear_w4a4_exact_reference`` (``src/orbitquant/kernels/executorch_vulkan.py:
+    15-61``): ``(sum_k lut[16 a + w]) * token_norm * row_norm + bias`` in fp32, rounded to
+    ``x``'s dtype.  The table entries are added one by one in ascending k (the reference sums
+    with ``torch.sum``, whose order is unspecified; the difference is fp32 summation noise).
+    Activation indices and token norms come from ``quantize_activations`` above (the native CPU
+    pipeline's order) rather than from the reference's torch expressions.  numpy; small sizes."""
+    import numpy as np
+
+    k = x.shape[-1]
+    x2 = x.contiguous().reshape(-1, k)
+    _, codes, norms = quantize_activations(x2, perm, signs, block, act_boundaries, act_centroids,
+                                           eps=eps, norm_order=norm_order)
+    a = codes.numpy().astype(np.int64)
+    w = unpack(packed, 4, out_features * k).numpy().astype(np.int64).reshape(out_features, k)
+    lut = pair_lut.to(torch.float32).numpy()
+    acc = np.zeros((a.shape[0], out_features), dtype=np.float32)
+    for kk in range(k):
+        acc += lut[a[:, kk][:, None] * 16 + w[:, kk][None, :]]
+    rn = row_norms.to(torch.float32).numpy()
+    out = (acc * norms.numpy()[:, None]).astype(np.float32) * rn[None, :]
+    if bias is not None:
+        out = out + bias.to(torch.float32).numpy()[None, :]
+    y32 = torch.from_numpy(out.astype(np.float32))
+    return y32.to(x.dtype).reshape(*x.shape[:-1], out_features), y32.reshape(*x.shape[:-1], out_features)
+
+
+def int8_surrogate_linear(x, packed, row_norms, bias, *, perm, signs, block, act_boundaries,
+                          act_centroids, act_codes, act_scale, w_codes, w_scale, w_bits, out_features,
+                          eps=1e-10, norm_order=NORM_AVX512):
+    """The reference's integer matmul (``packed_matmul.cu:744-1009``, epilogue ``:976-1007``):
+    ``(sum_k act_codes[a] * w_codes[w]) * token_norm * row_norm * (s_a * s_w) + bias`` with an
+    int32 sum, rounded to bf16.  numpy; small sizes."""
+    import numpy as np
+
+    k = x.shape[-1]
+    x2 = x.contiguous().reshape(-1, k)
+    _, codes, norms = quantize_activations(x2, perm, signs, block, act_boundaries, act_centroids,
+                                           eps=eps, norm_order=norm_order)
+    a = act_codes.numpy().astype(np.int64)[codes.numpy().astype(np.int64)]
+    w_idx = unpack(packed, w_bits, out_features * k).numpy().astype(np.int64).reshape(out_features, k)
+    w = w_codes.numpy().astype(np.int64)[w_idx]
+    acc = (a @ w.T).astype(np.float32)                      # exact: |sum| < 2^24 for these sizes
+    scale = np.float32(np.float32(act_scale) * np.float32(w_scale))
+    rn = row_norms.to(torch.float32).numpy()
+    out = acc * (norms.numpy() * scale)[:, None].astype(np.float32) * rn[None, :]
+    if bias is not None:
+        out = out + bias.to(torch.float32).numpy()[None, :]
+    y32 = torch.from_numpy(out.astype(np.float32))
+    return y32.to(torch.bfloat16).reshape(*x.shape[:-1], out_features), y32.reshape(*x.shape[:-1], out_features)

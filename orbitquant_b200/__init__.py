@@ -10,6 +10,7 @@ from .artifacts import load_orbitquant_artifact
 from .codebooks import LloydMaxCodebook, get_codebook
 from .config import OrbitQuantConfig
 from .functional import quantize_activations
+from .int8_surrogate import fit_int8_centroid_surrogate
 from .layers import OrbitQuantLinear, quantize_weight
 from .packing import pack_lowbit, packed_length, unpack_lowbit
 from .rotations import RPBHRotation, fwht, get_rpbh_rotation
@@ -19,7 +20,7 @@ __all__ = [
     "RTNInt4Linear",
     "quantize_adaln_weight",
     "LloydMaxCodebook", "OrbitQuantConfig", "OrbitQuantLinear", "RPBHRotation", "fwht",
-    "get_codebook", "get_rpbh_rotation", "pack_lowbit", "packed_length", "quantize_activations",
+    "fit_int8_centroid_surrogate", "get_codebook", "get_rpbh_rotation", "pack_lowbit", "packed_length", "quantize_activations",
     "quantize_weight", "unpack_lowbit",
 ]
 __version__ = "0.1.0"

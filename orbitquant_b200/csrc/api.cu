@@ -49,7 +49,15 @@ int launch_rotate_quantize(const void *x, int x_dtype, int64_t rows, int64_t dim
                            void *x_q, uint8_t *codes, float *norms, float *f16_row_scale,
                            const float *w_centroids, int w_bits, float *table_scale_out,
                            int *zero_words, int zero_count, cudaStream_t stream,
-                           const float *given_norms = nullptr);
+                           const float *given_norms = nullptr, const int8_t *code_map = nullptr);
+int launch_expand_packed_a4(const uint8_t *packed_act, const float *token_norms, const int8_t *act_codes,
+                            const int8_t *w_codes, int w_levels, float scale, int64_t rows, int64_t dim,
+                            void *out_f16, float *row_scale, float *table_scale, float *w_code_floats,
+                            cudaStream_t stream);
+int launch_pair_lut(void *out, int out_dtype, const uint8_t *codes, const float *token_norms,
+                    const uint8_t *packed, const void *row_norms_bf16, const float *pair_lut,
+                    const void *bias, int bias_dtype, int64_t rows, int64_t in_features,
+                    int64_t out_features, cudaStream_t stream);
 int launch_weight_row_norms(const void *w, int dtype, int64_t rows, int64_t dim, float *norms_f32,
                             void *norms_bf16, cudaStream_t stream);
 int launch_norms_to_bf16(const float *norms, int64_t rows, void *out, cudaStream_t stream);
@@ -317,6 +325,150 @@ int oq_quantize_activations(const void *x, int x_dtype, int64_t rows, int64_t di
   return launch_rotate_quantize(x, x_dtype, rows, dim, perm, signs, block, boundaries, centroids,
                                 bits, eps, x_q, codes, norms, nullptr, nullptr, 0, nullptr, nullptr, 0,
                                 static_cast<cudaStream_t>(stream));
+}
+
+size_t oq_quantize_activations_packed_w4_workspace_bytes(int64_t rows, int64_t dim) {
+  return rows <= 0 || dim <= 0 ? 0 : align_up(static_cast<size_t>(rows) * dim, 256);
+}
+
+int oq_quantize_activations_packed_w4(const void *x, int x_dtype, int64_t rows, int64_t dim,
+                                      const int32_t *perm, const int8_t *signs, int64_t block,
+                                      const float *boundaries, const float *centroids, float eps,
+                                      uint8_t *packed_out, float *norms_out, void *workspace,
+                                      size_t workspace_bytes, void *stream) {
+  OQ_CHECK_ARG(dim % 2 == 0, "the packed 4-bit output needs an even in_features");
+  if (rows == 0) {
+    return OQ_OK;
+  }
+  OQ_CHECK_ARG(packed_out != nullptr && norms_out != nullptr, "null device pointer");
+  const size_t need = oq_quantize_activations_packed_w4_workspace_bytes(rows, dim);
+  if (workspace == nullptr || workspace_bytes < need) {
+    return fail(OQ_ERR_WORKSPACE, "workspace of %zu bytes given, %zu needed", workspace_bytes, need);
+  }
+  if (int rc = check_device()) {
+    return rc;
+  }
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  uint8_t *codes = static_cast<uint8_t *>(workspace);
+  if (int rc = launch_rotate_quantize(x, x_dtype, rows, dim, perm, signs, block, boundaries, centroids,
+                                      4, eps, nullptr, codes, norms_out, nullptr, nullptr, 0, nullptr,
+                                      nullptr, 0, s)) {
+    return rc;
+  }
+  return launch_pack(codes, 4, rows * dim, packed_out, s);
+}
+
+int oq_quantize_activations_int8(const void *x, int x_dtype, int64_t rows, int64_t dim,
+                                 const int32_t *perm, const int8_t *signs, int64_t block,
+                                 const float *boundaries, const float *centroids, int bits,
+                                 const int8_t *act_codes, float eps, int8_t *codes_out,
+                                 float *norms_out, void *stream) {
+  if (rows == 0) {
+    return OQ_OK;
+  }
+  OQ_CHECK_ARG(act_codes != nullptr && codes_out != nullptr && norms_out != nullptr, "null device pointer");
+  if (int rc = check_device()) {
+    return rc;
+  }
+  return launch_rotate_quantize(x, x_dtype, rows, dim, perm, signs, block, boundaries, centroids, bits,
+                                eps, nullptr, reinterpret_cast<uint8_t *>(codes_out), norms_out, nullptr,
+                                nullptr, 0, nullptr, nullptr, 0, static_cast<cudaStream_t>(stream),
+                                nullptr, act_codes);
+}
+
+size_t oq_matmul_packed_w4a4_int8_workspace_bytes(int64_t rows, int64_t in_features) {
+  if (rows <= 0 || in_features <= 0) {
+    return 0;
+  }
+  return tcgen05_head_bytes(rows, in_features) + 256 * sizeof(float);
+}
+
+int oq_matmul_packed_w4a4_int8(void *out, const uint8_t *packed_act, const uint8_t *packed_weight,
+                               int64_t packed_weight_bytes, int weight_bits, const float *token_norms,
+                               const void *row_norms_bf16, const int8_t *act_codes,
+                               const int8_t *weight_codes, const void *bias, int bias_dtype,
+                               float act_scale, float weight_scale, int64_t rows, int64_t in_features,
+                               int64_t out_features, void *workspace, size_t workspace_bytes,
+                               void *stream) {
+  OQ_CHECK_ARG(rows >= 0 && in_features > 0 && out_features >= 0, "negative or empty shape");
+  OQ_CHECK_ARG(weight_bits == 2 || weight_bits == 3 || weight_bits == 4 || weight_bits == 6,
+               "the INT8 surrogate exists for 2-, 3-, 4- and 6-bit weights");
+  OQ_CHECK_ARG(bias == nullptr || valid_dtype(bias_dtype), "bias must be float32, float16, or bfloat16");
+  OQ_CHECK_ARG(packed_weight_bytes >= (out_features * in_features * weight_bits + 7) / 8,
+               "packed weights are too short");
+  if (rows == 0 || out_features == 0) {
+    return OQ_OK;
+  }
+  OQ_CHECK_ARG(out && packed_act && packed_weight && token_norms && row_norms_bf16 && act_codes && weight_codes,
+               "null device pointer");
+  if (!tcgen05_gemm_supported(rows, in_features, out_features, weight_bits, OQ_DTYPE_BF16, OQ_WEIGHT_CENTROID)) {
+    return fail(OQ_ERR_UNSUPPORTED, "the INT8-surrogate matmul needs in_features %% 64 == 0");
+  }
+  const size_t need = oq_matmul_packed_w4a4_int8_workspace_bytes(rows, in_features);
+  if (workspace == nullptr || workspace_bytes < need) {
+    return fail(OQ_ERR_WORKSPACE, "workspace of %zu bytes given, %zu needed", workspace_bytes, need);
+  }
+  OQ_CHECK_ARG(aligned16(workspace), "workspace must be 16-byte aligned");
+  if (int rc = check_device()) {
+    return rc;
+  }
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  unsigned char *ws = static_cast<unsigned char *>(workspace);
+  float *row_scale = reinterpret_cast<float *>(ws + f16_operand_bytes(rows, in_features));
+  float *table_scale = row_scale + rows;
+  float *code_floats = reinterpret_cast<float *>(ws + tcgen05_head_bytes(rows, in_features));
+  if (int rc = launch_expand_packed_a4(packed_act, token_norms, act_codes, weight_codes, 1 << weight_bits,
+                                       act_scale * weight_scale, rows, in_features, workspace, row_scale,
+                                       table_scale, code_floats, s)) {
+    return rc;
+  }
+  // integer codes are exact in f16; the table scale is 1 and the per-token factor carries
+  // token_norm * s_a * s_w, so the ordinary epilogue computes the surrogate's
+  return launch_tcgen05_gemm(out, workspace, row_scale, table_scale, rows, in_features, out_features,
+                             packed_weight, weight_bits, row_norms_bf16, code_floats, bias, bias_dtype, s);
+}
+
+size_t oq_linear_w4a4_pair_lut_workspace_bytes(int64_t rows, int64_t in_features) {
+  if (rows <= 0 || in_features <= 0) {
+    return 0;
+  }
+  return align_up(static_cast<size_t>(rows) * in_features, 256) + align_up(static_cast<size_t>(rows) * 4, 256);
+}
+
+int oq_linear_w4a4_pair_lut(void *out, const void *x, int dtype, int64_t rows, int64_t in_features,
+                            int64_t out_features, const uint8_t *packed, int64_t packed_bytes,
+                            const void *row_norms_bf16, const void *bias, int bias_dtype,
+                            const int32_t *perm, const int8_t *signs, int64_t block,
+                            const float *act_boundaries, const float *act_centroids,
+                            const float *pair_lut, float eps, void *workspace, size_t workspace_bytes,
+                            void *stream) {
+  OQ_CHECK_ARG(valid_dtype(dtype), "x must be float32, float16, or bfloat16");
+  OQ_CHECK_ARG(rows >= 0 && in_features > 0 && out_features >= 0, "negative or empty shape");
+  OQ_CHECK_ARG(in_features % 2 == 0, "in_features must be even");
+  OQ_CHECK_ARG(bias == nullptr || valid_dtype(bias_dtype), "bias must be float32, float16, or bfloat16");
+  OQ_CHECK_ARG(packed_bytes >= out_features * in_features / 2, "packed weights are too short");
+  if (rows == 0 || out_features == 0) {
+    return OQ_OK;
+  }
+  OQ_CHECK_ARG(out && x && packed && row_norms_bf16 && pair_lut, "null device pointer");
+  const size_t need = oq_linear_w4a4_pair_lut_workspace_bytes(rows, in_features);
+  if (workspace == nullptr || workspace_bytes < need) {
+    return fail(OQ_ERR_WORKSPACE, "workspace of %zu bytes given, %zu needed", workspace_bytes, need);
+  }
+  if (int rc = check_device()) {
+    return rc;
+  }
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  uint8_t *codes = static_cast<uint8_t *>(workspace);
+  float *norms = reinterpret_cast<float *>(static_cast<unsigned char *>(workspace) +
+                                           align_up(static_cast<size_t>(rows) * in_features, 256));
+  if (int rc = launch_rotate_quantize(x, dtype, rows, in_features, perm, signs, block, act_boundaries,
+                                      act_centroids, 4, eps, nullptr, codes, norms, nullptr, nullptr, 0,
+                                      nullptr, nullptr, 0, s)) {
+    return rc;
+  }
+  return launch_pair_lut(out, dtype, codes, norms, packed, row_norms_bf16, pair_lut, bias, bias_dtype,
+                         rows, in_features, out_features, s);
 }
 
 int oq_gemm_tcgen05_supported(int64_t rows, int64_t in_features, int64_t out_features, int bits,

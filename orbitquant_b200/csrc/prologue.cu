@@ -63,6 +63,10 @@ struct PrologueParams {
   // GIVEN, nothing is pre-scaled, and the direction is (fwht * 1/sqrt(block)) / max(norm, eps)
   // -- a true division, after the transform, as the reference's torch expression has it.
   const float *given_norms;
+  // When set, the code output holds code_map[index] instead of the index: the INT8 surrogate
+  // codes of the reference's integer matmul (orbitquant_rpbh_quantize_int8_kernel,
+  // packed_matmul.cu:659-742).  General kernel only.
+  const int8_t *code_map;
   // Few rows (decode): a row is split over `slices` CTAs along whole rotation blocks.  Every
   // CTA still loads the row and computes its norm (both are needed everywhere and cheap), but
   // transforms, quantises and stores only its own blocks.  1 = no split.  Fast kernel only.
@@ -116,7 +120,7 @@ __device__ __forceinline__ void emit(const PrologueParams &p, void *stage_row, u
     Scalar<DTYPE>::store(stage_row, i, q);
   }
   if (codes_row != nullptr) {
-    codes_row[i] = static_cast<uint8_t>(idx);
+    codes_row[i] = p.code_map != nullptr ? static_cast<uint8_t>(p.code_map[idx]) : static_cast<uint8_t>(idx);
   }
 }
 
@@ -514,7 +518,7 @@ int launch_rotate_quantize(const void *x, int x_dtype, int64_t rows, int64_t dim
                            void *x_q, uint8_t *codes, float *norms, float *f16_row_scale,
                            const float *w_centroids, int w_bits, float *table_scale_out,
                            int *zero_words, int zero_count, cudaStream_t stream,
-                           const float *given_norms) {
+                           const float *given_norms, const int8_t *code_map) {
   OQ_CHECK_ARG(table_scale_out == nullptr || (w_centroids != nullptr && w_bits >= 1 && w_bits <= 8),
                "the table scale search needs the weight codebook");
   OQ_CHECK_ARG(f16_row_scale == nullptr || (x_dtype != OQ_DTYPE_F32 && x_q != nullptr),
@@ -544,11 +548,12 @@ int launch_rotate_quantize(const void *x, int x_dtype, int64_t rows, int64_t dim
   OQ_CHECK_CUDA(cudaDeviceGetAttribute(&max_smem, cudaDevAttrMaxSharedMemoryPerBlockOptin, device));
 
   // Kernel choice.  The prologue_kernel tunable pins it: 0 = general, 1 = multi-token CTA,
-  // 2 = warp-per-block; otherwise large token counts take the warp-per-block kernel.
+  // 2 = warp-per-block; otherwise 2048 tokens and more take the warp-per-block kernel (measured
+  // cross-over at 3072 features: 14.2 against 13.5 us at 1184 tokens, 20.6 against 24.5 at 2368).
   const int forced = tunable(OQ_TUNE_PROLOGUE_KERNEL);
   const bool plain_output = codes == nullptr && norms == nullptr && x_q != nullptr && given_norms == nullptr;
   if (plain_output && warp_prologue_supported(x_dtype, dim, block, bits) &&
-      (forced == 2 || (forced < 0 && rows >= 2 * static_cast<int64_t>(sm_count)))) {
+      (forced == 2 || (forced < 0 && rows >= 2048))) {
     int batch_rows = 0;
     int slots = 0;
     int ctas_per_sm = 0;
@@ -647,6 +652,7 @@ int launch_rotate_quantize(const void *x, int x_dtype, int64_t rows, int64_t dim
   p.zero_words = zero_words;
   p.zero_count = zero_words != nullptr ? zero_count : 0;
   p.given_norms = given_norms;
+  p.code_map = code_map;
   p.slices = 1;
 
   if (fast != nullptr && rows * 2 <= sm_count) {

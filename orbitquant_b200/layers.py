@@ -269,6 +269,8 @@ class OrbitQuantLinear(nn.Module):
         self._derived_constants_valid = False
         self._bias_cache = None
         self._norms_cache = None
+        self._int8_surrogate_cache = None
+        self._pair_lut_cache = None
         return result
 
     def _ensure_derived_constants(self, device: torch.device) -> None:
@@ -327,6 +329,10 @@ class OrbitQuantLinear(nn.Module):
         self.last_effective_runtime_mode = "native_packed_matmul"
         self.last_activation_kernel_backend = "orbit_b200"
         self.last_forward_device_type = "cuda"
+        if self.weight_mode == "int8_surrogate":
+            return self._forward_int8_surrogate(x)
+        if self.weight_mode == "pair_lut":
+            return self._forward_pair_lut(x)
         return native.linear_forward(
             x, packed, self._row_norms_for(device), self._bias_for(device),
             permutation=self._rotation_permutation, signs=self._rotation_signs,
@@ -338,6 +344,55 @@ class OrbitQuantLinear(nn.Module):
             eps=self.activation_eps,
             weight_mode=native.WEIGHT_MODE_NAMES[self.weight_mode],
             kernel=native.KERNEL_NAMES[self.kernel])
+
+    def _int8_surrogate_constants(self, device: torch.device):
+        """INT8 code tables and scales of both codebooks (reference ``layers.py:811-835``)."""
+        cache = getattr(self, "_int8_surrogate_cache", None)
+        if cache is None or cache[0] != str(device):
+            from .int8_surrogate import fit_int8_centroid_surrogate
+            a_codes, a_scale = fit_int8_centroid_surrogate(self.activation_codebook.centroids)
+            w_codes, w_scale = fit_int8_centroid_surrogate(self.weight_codebook.centroids)
+            cache = (str(device), a_codes.to(device), a_scale, w_codes.to(device), w_scale)
+            self._int8_surrogate_cache = cache
+        return cache[1:]
+
+    def _forward_int8_surrogate(self, x: torch.Tensor) -> torch.Tensor:
+        """The reference's integer path for W4A4 / W2A4 (``layers.py:1097-1352``): packed 4-bit
+        activation codes, INT8 code tables, integer contraction, rescale.  Approximate (the
+        codes are rounded centroids); selected with ``module.weight_mode = "int8_surrogate"``."""
+        if self.activation_bits != 4 or self.weight_bits not in (2, 3, 4, 6):
+            raise ValueError("the INT8 surrogate path takes 4-bit activations and 2/3/4/6-bit weights")
+        device = x.device
+        a_codes, a_scale, w_codes, w_scale = self._int8_surrogate_constants(device)
+        packed_x, token_norms = native.quantize_activations_packed_w4(
+            x, self._rotation_permutation, self._rotation_signs, self._activation_codebook_centroids,
+            self._activation_codebook_boundaries, eps=self.activation_eps,
+            block_size=self.rotation.block_size)
+        self.last_activation_kernel_backend = "orbit_b200_int8_surrogate"
+        y = native.matmul_packed_w4a4_int8(
+            packed_x, self.packed_weight_indices, token_norms, self._row_norms_for(device), a_codes,
+            w_codes, act_scale=a_scale, weight_scale=w_scale, out_features=self.out_features,
+            in_features=self.in_features, weight_bits=self.weight_bits, bias=self._bias_for(device))
+        return y if y.dtype == x.dtype else y.to(x.dtype)
+
+    def _forward_pair_lut(self, x: torch.Tensor) -> torch.Tensor:
+        """Exact W4A4 through the 256-entry pair-product table
+        (``src/orbitquant/kernels/executorch_vulkan.py:15-61``); ``weight_mode = "pair_lut"``."""
+        if self.activation_bits != 4 or self.weight_bits != 4:
+            raise ValueError("the pair-product table exists for W4A4 only")
+        device = x.device
+        lut = getattr(self, "_pair_lut_cache", None)
+        if lut is None or lut.device != device:
+            lut = (self.activation_codebook.centroids.float()[:, None]
+                   * self.weight_codebook.centroids.float()[None, :]).flatten().contiguous().to(device)
+            self._pair_lut_cache = lut
+        return native.linear_w4a4_pair_lut(
+            x, self.packed_weight_indices, self._row_norms_for(device), self._bias_for(device),
+            permutation=self._rotation_permutation, signs=self._rotation_signs,
+            block_size=self.rotation.block_size,
+            act_boundaries=self._activation_codebook_boundaries,
+            act_centroids=self._activation_codebook_centroids, pair_lut=lut,
+            out_features=self.out_features, eps=self.activation_eps)
 
     def forward_scatter(self, x: torch.Tensor, out_ptrs, out_ld: int, out_col: int) -> None:
         """Forward of a column shard whose result goes straight into every buffer of

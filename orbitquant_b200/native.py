@@ -36,6 +36,17 @@ _SIGNATURES = {
     "oq_dequantize_weight": (_int, [_vp, _int, _i64, _i64, _vp, _vp, _vp, _int, _vp]),
     "oq_quantize_activations": (_int, [_vp, _int, _i64, _i64, _vp, _vp, _i64, _vp, _vp, _int,
                                        _f32, _vp, _vp, _vp, _vp]),
+    "oq_quantize_activations_packed_w4_workspace_bytes": (_sz, [_i64, _i64]),
+    "oq_quantize_activations_packed_w4": (_int, [_vp, _int, _i64, _i64, _vp, _vp, _i64, _vp, _vp, _f32,
+                                                 _vp, _vp, _vp, _sz, _vp]),
+    "oq_quantize_activations_int8": (_int, [_vp, _int, _i64, _i64, _vp, _vp, _i64, _vp, _vp, _int, _vp,
+                                            _f32, _vp, _vp, _vp]),
+    "oq_matmul_packed_w4a4_int8_workspace_bytes": (_sz, [_i64, _i64]),
+    "oq_matmul_packed_w4a4_int8": (_int, [_vp, _vp, _vp, _i64, _int, _vp, _vp, _vp, _vp, _vp, _int, _f32,
+                                          _f32, _i64, _i64, _i64, _vp, _sz, _vp]),
+    "oq_linear_w4a4_pair_lut_workspace_bytes": (_sz, [_i64, _i64]),
+    "oq_linear_w4a4_pair_lut": (_int, [_vp, _vp, _int, _i64, _i64, _i64, _vp, _i64, _vp, _vp, _int, _vp,
+                                       _vp, _i64, _vp, _vp, _vp, _f32, _vp, _sz, _vp]),
     "oq_matmul_packed_weight": (_int, [_vp, _vp, _int, _i64, _i64, _i64, _vp, _i64, _int, _vp,
                                        _vp, _vp, _int, _int, _int, _vp, _sz, _vp]),
     "oq_matmul_workspace_bytes": (_sz, [_i64, _i64, _i64, _int, _int, _int, _int]),
@@ -419,4 +430,126 @@ def rtn_int4_linear_forward(x, packed, scales, bias, *, out_features, group_size
         _check(lib.oq_rtn_int4_linear_forward(
             _ptr(out), _ptr(x2), rows, in_features, out_features, _ptr(packed), packed.numel(),
             _ptr(scales), int(group_size), _ptr(bias), bias_code, _ptr(ws), ws_bytes, _stream(device)))
+    return out.reshape(*x.shape[:-1], out_features)
+
+
+def _activation_constants(x, permutation, signs, centroids, boundaries):
+    device = x.device
+    return (permutation.to(device=device, dtype=torch.int32).contiguous(),
+            signs.to(device=device, dtype=torch.int8).contiguous(),
+            centroids.to(device=device, dtype=torch.float32).contiguous(),
+            boundaries.to(device=device, dtype=torch.float32).contiguous())
+
+
+def quantize_activations_packed_w4(x, permutation, signs, centroids, boundaries, *, eps, block_size):
+    """4-bit activation indices packed two per byte ``[..., K/2]`` (low nibble = even k) and the
+    fp32 token norms -- the activation stream of the integer matmuls
+    (reference wrapper ``orbitquant_packed_matmul/__init__.py``: ``quantize_activations_packed_w4``)."""
+    _require_cuda("x", x)
+    if x.dtype not in DTYPE_CODES:
+        raise ValueError("x must be float32, float16, or bfloat16")
+    if centroids.numel() != 16 or boundaries.numel() != 15:
+        raise ValueError("the packed 4-bit output needs a 4-bit activation codebook")
+    dim = x.shape[-1]
+    values = x.contiguous().reshape(-1, dim)
+    rows = values.shape[0]
+    device = x.device
+    perm, sgn, cent, bnd = _activation_constants(x, permutation, signs, centroids, boundaries)
+    packed = torch.empty((rows, dim // 2), dtype=torch.uint8, device=device)
+    norms = torch.empty((rows,), dtype=torch.float32, device=device)
+    lib = load()
+    ws_bytes = lib.oq_quantize_activations_packed_w4_workspace_bytes(rows, dim)
+    ws = torch.empty(max(ws_bytes, 16), dtype=torch.uint8, device=device)
+    with torch.cuda.device(device):
+        _check(lib.oq_quantize_activations_packed_w4(
+            _ptr(values), DTYPE_CODES[x.dtype], rows, dim, _ptr(perm), _ptr(sgn), int(block_size),
+            _ptr(bnd), _ptr(cent), float(eps), _ptr(packed), _ptr(norms), _ptr(ws), ws_bytes,
+            _stream(device)))
+    return packed.reshape(*x.shape[:-1], dim // 2), norms.reshape(x.shape[:-1])
+
+
+def quantize_activations_int8(x, permutation, signs, centroids, boundaries, act_codes, *, eps, block_size):
+    """``act_codes[index]`` as int8 ``[..., K]`` and the fp32 token norms (reference wrapper
+    ``quantize_activations_int8``)."""
+    _require_cuda("x", x)
+    if x.dtype not in DTYPE_CODES:
+        raise ValueError("x must be float32, float16, or bfloat16")
+    dim = x.shape[-1]
+    values = x.contiguous().reshape(-1, dim)
+    rows = values.shape[0]
+    device = x.device
+    bits = int(centroids.numel()).bit_length() - 1
+    perm, sgn, cent, bnd = _activation_constants(x, permutation, signs, centroids, boundaries)
+    table = act_codes.to(device=device, dtype=torch.int8).contiguous()
+    if table.numel() < 1 << bits:
+        raise ValueError("act_codes must hold 2^bits entries")
+    codes = torch.empty((rows, dim), dtype=torch.int8, device=device)
+    norms = torch.empty((rows,), dtype=torch.float32, device=device)
+    with torch.cuda.device(device):
+        _check(load().oq_quantize_activations_int8(
+            _ptr(values), DTYPE_CODES[x.dtype], rows, dim, _ptr(perm), _ptr(sgn), int(block_size),
+            _ptr(bnd), _ptr(cent), bits, _ptr(table), float(eps), _ptr(codes), _ptr(norms),
+            _stream(device)))
+    return codes.reshape(x.shape), norms.reshape(x.shape[:-1])
+
+
+def matmul_packed_w4a4_int8(packed_act, packed_weight, token_norms, row_norms, act_codes, weight_codes, *,
+                            act_scale, weight_scale, out_features, in_features, weight_bits=4, bias=None):
+    """The INT8-surrogate matmul on packed 4-bit activations (reference wrapper
+    ``matmul_packed_w4a4_int8``); bf16 output."""
+    _require_cuda("packed_act", packed_act)
+    device = packed_act.device
+    pa = packed_act.to(torch.uint8).contiguous().reshape(-1, in_features // 2)
+    rows = pa.shape[0]
+    pw = packed_weight.to(device=device, dtype=torch.uint8).contiguous()
+    tn = token_norms.to(device=device, dtype=torch.float32).contiguous().reshape(-1)
+    rn = row_norms.to(device=device, dtype=torch.bfloat16).contiguous()
+    ac = act_codes.to(device=device, dtype=torch.int8).contiguous()
+    wc = weight_codes.to(device=device, dtype=torch.int8).contiguous()
+    bias_t = None if bias is None else bias.to(device=device).contiguous()
+    if bias_t is not None and bias_t.dtype not in DTYPE_CODES:
+        bias_t = bias_t.to(torch.float32)
+    out = torch.empty((rows, out_features), dtype=torch.bfloat16, device=device)
+    lib = load()
+    ws_bytes = lib.oq_matmul_packed_w4a4_int8_workspace_bytes(rows, in_features)
+    ws = torch.empty(max(ws_bytes, 16), dtype=torch.uint8, device=device)
+    with torch.cuda.device(device):
+        _check(lib.oq_matmul_packed_w4a4_int8(
+            _ptr(out), _ptr(pa), _ptr(pw), pw.numel(), int(weight_bits), _ptr(tn), _ptr(rn), _ptr(ac),
+            _ptr(wc), _ptr(bias_t), 0 if bias_t is None else DTYPE_CODES[bias_t.dtype],
+            float(act_scale), float(weight_scale), rows, in_features, out_features, _ptr(ws), ws_bytes,
+            _stream(device)))
+    return out.reshape(*packed_act.shape[:-1], out_features)
+
+
+def linear_w4a4_pair_lut(x, packed, row_norms, bias, *, permutation, signs, block_size, act_boundaries,
+                         act_centroids, pair_lut, out_features, eps):
+    """The exact W4A4 linear through the 256-entry pair-product table (the arithmetic of the
+    reference's ``orbitquant_vulkan::linear_w4a4_exact``); output in ``x``'s dtype."""
+    _require_cuda("x", x)
+    if x.dtype not in DTYPE_CODES:
+        raise ValueError("x must be float32, float16, or bfloat16")
+    in_features = x.shape[-1]
+    device = x.device
+    x2 = x.contiguous().reshape(-1, in_features)
+    rows = x2.shape[0]
+    perm, sgn, cent, bnd = _activation_constants(x, permutation, signs, act_centroids, act_boundaries)
+    lut = pair_lut.to(device=device, dtype=torch.float32).contiguous()
+    if lut.numel() != 256:
+        raise ValueError("pair_lut must hold 256 entries")
+    pw = packed.to(device=device, dtype=torch.uint8).contiguous()
+    rn = row_norms.to(device=device, dtype=torch.bfloat16).contiguous()
+    bias_t = None if bias is None else bias.to(device=device).contiguous()
+    if bias_t is not None and bias_t.dtype not in DTYPE_CODES:
+        bias_t = bias_t.to(torch.float32)
+    out = torch.empty((rows, out_features), dtype=x.dtype, device=device)
+    lib = load()
+    ws_bytes = lib.oq_linear_w4a4_pair_lut_workspace_bytes(rows, in_features)
+    ws = torch.empty(max(ws_bytes, 16), dtype=torch.uint8, device=device)
+    with torch.cuda.device(device):
+        _check(lib.oq_linear_w4a4_pair_lut(
+            _ptr(out), _ptr(x2), DTYPE_CODES[x.dtype], rows, in_features, out_features, _ptr(pw),
+            pw.numel(), _ptr(rn), _ptr(bias_t), 0 if bias_t is None else DTYPE_CODES[bias_t.dtype],
+            _ptr(perm), _ptr(sgn), int(block_size), _ptr(bnd), _ptr(cent), _ptr(lut), float(eps),
+            _ptr(ws), ws_bytes, _stream(device)))
     return out.reshape(*x.shape[:-1], out_features)
