@@ -500,11 +500,12 @@ def measure_decode(workload, rows, device, steps, warmup, with_e2e=True):
 
 
 def decode_kernel_names(specs, rows, w_bits):
-    from orbitquant_b200 import native
+    from orbitquant_b200 import get_rpbh_rotation, native
 
     names = set()
     for l in specs:
-        names.add(native.forward_kernel_name(rows, l.k, l.n, w_bits))
+        block = get_rpbh_rotation(l.k, 0, "paper").block_size
+        names.add(native.forward_kernel_name(rows, l.k, l.n, w_bits, l.a_bits, block))
     return sorted(names)
 
 

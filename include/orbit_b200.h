@@ -247,7 +247,8 @@ int oq_linear_w4a4_pair_lut(void *out, const void *x, int dtype, int64_t rows, i
  * OrbitQuantLinear.last_effective_runtime_mode / last_activation_kernel_backend
  * (src/orbitquant/layers.py:1079-1455); here it can be asked up front. */
 const char *oq_linear_kernel_name(int64_t rows, int64_t in_features, int64_t out_features,
-                                  int weight_bits, int dtype, int weight_mode, int kernel);
+                                  int weight_bits, int act_bits, int64_t block, int dtype,
+                                  int weight_mode, int kernel);
 
 /* y = OrbitQuantLinear(x): oq_quantize_activations into workspace, then
  * oq_matmul_packed_weight.  Replaces OrbitQuantLinear._forward_impl on CUDA

@@ -115,6 +115,13 @@ int launch_tcgen05_rtn_int4(void *out, const void *x_bf16, int64_t rows, int64_t
                             int64_t out_features, const uint8_t *packed, const void *scales_bf16,
                             const void *bias, int bias_dtype, void *workspace,
                             size_t workspace_bytes, cudaStream_t stream);
+bool decode_fused_supported(int64_t rows, int64_t in_features, int64_t out_features, int weight_bits,
+                            int act_bits, int dtype, int64_t block);
+int launch_decode_fused(void *out, const void *x, int64_t rows, int64_t in_features, int64_t out_features,
+                        const uint8_t *packed, const void *row_norms_bf16, const float *w_centroids,
+                        const void *bias, int bias_dtype, const int32_t *perm, const int8_t *signs,
+                        int64_t block, const float *act_boundaries, const float *act_centroids,
+                        int act_bits, float eps, int weight_mode, cudaStream_t stream);
 int read_gemm_status(int *status);
 int clear_gemm_status();
 int read_prologue_status(int *status);
@@ -190,6 +197,14 @@ bool use_stream_rows(int64_t rows, int64_t in_features, int64_t out_features, in
     return rows >= 1 && rows <= 16 && bits == 4 && dtype == OQ_DTYPE_BF16 && in_features % 128 == 0;
   }
   return fits;
+}
+
+// Decode-sized batches on small layers: the whole forward in one launch (decode_fused.cuh).
+// The fused_decode tunable set to 0 keeps the two-kernel path (for A/B timing).
+bool use_fused_decode(int kernel, int64_t rows, int64_t in_features, int64_t out_features, int weight_bits,
+                      int act_bits, int dtype, int64_t block) {
+  return kernel == OQ_KERNEL_AUTO && tunable(OQ_TUNE_FUSED_DECODE) != 0 &&
+         decode_fused_supported(rows, in_features, out_features, weight_bits, act_bits, dtype, block);
 }
 
 // Bytes of the f16 operand [rows, K] (256-aligned); the per-token factors follow it.
@@ -626,13 +641,17 @@ size_t oq_linear_workspace_bytes(int64_t rows, int64_t in_features, int64_t out_
 }
 
 const char *oq_linear_kernel_name(int64_t rows, int64_t in_features, int64_t out_features,
-                                  int weight_bits, int dtype, int weight_mode, int kernel) {
+                                  int weight_bits, int act_bits, int64_t block, int dtype,
+                                  int weight_mode, int kernel) {
   if (rows <= 0 || in_features <= 0 || out_features <= 0) {
     return "none";
   }
   const int mode = resolve_weight_mode(weight_mode);
   switch (choose_kernel(kernel, rows, in_features, out_features, weight_bits, dtype, mode)) {
     case OQ_KERNEL_SMALL_ROWS:
+      if (use_fused_decode(kernel, rows, in_features, out_features, weight_bits, act_bits, dtype, block)) {
+        return "decode_fused_kernel";
+      }
       return use_stream_rows(rows, in_features, out_features, weight_bits, dtype)
                  ? "rotate_quantize + stream_rows_w4_kernel"
                  : "rotate_quantize + small_rows_w4_kernel";
@@ -703,6 +722,14 @@ int oq_linear_forward(void *out, const void *x, int dtype, int64_t rows, int64_t
     return tcgen05_matmul(out, workspace, workspace_bytes, rows, in_features, out_features, packed,
                           weight_bits, dtype, mode, row_norms_bf16, weight_centroids, bias,
                           bias_dtype, s);
+  }
+  if (chosen == OQ_KERNEL_SMALL_ROWS &&
+      use_fused_decode(kernel, rows, in_features, out_features, weight_bits, act_bits, dtype, block)) {
+    OQ_CHECK_ARG(out && x && packed && row_norms_bf16 && weight_centroids && perm && signs &&
+                     act_boundaries && act_centroids, "null device pointer");
+    return launch_decode_fused(out, x, rows, in_features, out_features, packed, row_norms_bf16,
+                               weight_centroids, bias, bias_dtype, perm, signs, block, act_boundaries,
+                               act_centroids, act_bits, eps, mode, s);
   }
   if (int rc = launch_rotate_quantize(x, dtype, rows, in_features, perm, signs, block, act_boundaries,
                                       act_centroids, act_bits, eps, workspace, nullptr, nullptr,

@@ -448,6 +448,7 @@ rotate_quantize_kernel(const PrologueParams p) {
 
 #include "prologue_fast.cuh"
 #include "prologue_warp.cuh"
+#include "decode_fused.cuh"
 
 namespace oq {
 namespace {

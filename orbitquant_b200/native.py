@@ -71,7 +71,7 @@ _SIGNATURES = {
     "oq_rtn_int4_workspace_bytes": (_sz, [_i64, _i64, _i64]),
     "oq_static_scratch_bytes": (_sz, []),
     "oq_linear_workspace_bytes": (_sz, [_i64, _i64, _i64, _int, _int, _int, _int]),
-    "oq_linear_kernel_name": (ctypes.c_char_p, [_i64, _i64, _i64, _int, _int, _int, _int]),
+    "oq_linear_kernel_name": (ctypes.c_char_p, [_i64, _i64, _i64, _int, _int, _i64, _int, _int, _int]),
     "oq_gemm_device_status": (_int, [ctypes.POINTER(ctypes.c_int)]),
     "oq_gemm_clear_device_status": (_int, []),
 }
@@ -141,11 +141,12 @@ def set_tunable(name: str, value: int | None) -> None:
     _check(load().oq_set_tunable(name.encode(), -1 if value is None else int(value)))
 
 
-def forward_kernel_name(rows: int, in_features: int, out_features: int, weight_bits: int, *,
-                        dtype=torch.bfloat16, weight_mode=WEIGHT_AUTO, kernel=KERNEL_AUTO) -> str:
+def forward_kernel_name(rows: int, in_features: int, out_features: int, weight_bits: int,
+                        act_bits: int, block_size: int, *, dtype=torch.bfloat16,
+                        weight_mode=WEIGHT_AUTO, kernel=KERNEL_AUTO) -> str:
     """Which kernels ``linear_forward`` launches for this problem (``oq_linear_kernel_name``)."""
-    return load().oq_linear_kernel_name(rows, in_features, out_features, weight_bits,
-                                        DTYPE_CODES[dtype], weight_mode, kernel).decode()
+    return load().oq_linear_kernel_name(rows, in_features, out_features, weight_bits, act_bits,
+                                        int(block_size), DTYPE_CODES[dtype], weight_mode, kernel).decode()
 
 
 def gemm_device_status() -> int:
