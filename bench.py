@@ -893,6 +893,8 @@ def run_multi_gpu(args, device, rank, world, local_rank):
             return peers[i].tensor
         if fused_gather:
             peers[i].scatter(module, x)
+            if defer_wait:
+                return None
             peers[i].wait()
             return peers[i].tensor
         return gather_columns(module(x), layer.n)
@@ -910,13 +912,15 @@ def run_multi_gpu(args, device, rank, world, local_rank):
         gather_check = "bit-equal" if int(same.item()) == 1 else "MISMATCH"
 
     def step():
-        # the projections are independent here, so with the copy-engine gather each layer's
-        # transfers run under the next layer's kernels and are joined at the end
+        # the projections are independent here, so each layer's transfers (peer stores issued by
+        # the GEMM epilogue, or copy-engine copies) may still be landing while the next layer
+        # computes; the inter-rank barriers that complete them are joined at the end of the step
         outs = [sharded_forward(i, x, layers[i][0].gather, defer_wait=True) for i, x in enumerate(inputs)]
-        if dma_gather:
+        if dma_gather or fused_gather:
             for i, (layer, _m) in enumerate(layers):
                 if layer.gather:
                     peers[i].wait()
+                    outs[i] = peers[i].tensor
         return outs
 
     def barrier():
@@ -970,7 +974,8 @@ def run_multi_gpu(args, device, rank, world, local_rank):
             gather = ("copy engines (cudaMemcpy2DAsync into every rank's buffer) under the next "
                       "layer's kernels, barriers at the end of the step")
         elif fused_gather:
-            gather = "gemm epilogue stores into every rank's buffer (peer memory), one barrier per layer"
+            gather = ("gemm epilogue stores into every rank's buffer (peer memory); one barrier per "
+                      "gathered layer, joined at the end of the step (the projections are independent)")
         elif token_sharded:
             gather = "none (token-sharded)"
         else:
