@@ -588,13 +588,16 @@ def kernel_alone(layers, inputs, steps, peaks):
     torch.cuda.synchronize()
     kernel_ms = sum(e0.elapsed_time(e1) for e0, e1 in events)
     rows = inputs[0].shape[0]
+    names = sorted({native.forward_kernel_name(rows, l.k, m.out_features, l.w_bits, l.a_bits,
+                                               m.rotation.block_size).split(" + ")[-1]
+                    for l, m in layers})
     flops = sum(layer_flops(rows, l.k, m.out_features) for l, m in layers)
     achieved = flops * steps / (kernel_ms * 1e-3) / 1e12
     return {"bound": "tensor", "achieved": achieved, "peak": peaks["tflops_burst"], "unit": "TFLOP/s",
             "frac": achieved / peaks["tflops_burst"],
             "peak_sustained": peaks["tflops_sustained"],
             "frac_of_sustained": achieved / peaks["tflops_sustained"],
-            "peak_source": peaks["source"], "kernel": "gemm_w4_tcgen05_kernel",
+            "peak_source": peaks["source"], "kernel": " / ".join(names),
             "timed": "every launch alone between its own CUDA events",
             "avg_launch_us": kernel_ms * 1e3 / max(1, len(events)), "launches_timed": len(events)}
 

@@ -14,7 +14,7 @@ std::atomic<uint64_t> g_launch_count{0};
 namespace {
 const char *const kTunableNames[OQ_TUNE_COUNT] = {
     "TILE_N", "TILE_ORDER", "SKINNY", "STREAM_ROWS", "PROLOGUE_ROWS", "SKINNY_UNITS_PER_SM",
-    "SKINNY_MIN_ITERS", "FUSED_DECODE", "PROLOGUE_KERNEL"};
+    "SKINNY_MIN_ITERS", "FUSED_DECODE", "PROLOGUE_KERNEL", "PAIR"};
 std::atomic<int> g_tunables[OQ_TUNE_COUNT];
 std::once_flag g_tunables_once;
 
@@ -87,6 +87,7 @@ int launch_dequantize(const uint8_t *packed, int bits, int64_t out_features, int
                       int out_dtype, cudaStream_t stream);
 bool tcgen05_gemm_supported(int64_t rows, int64_t in_features, int64_t out_features, int bits,
                             int dtype, int weight_mode);
+const char *tcgen05_gemm_kernel_name(int64_t rows, int64_t out_features, int bits);
 int launch_rows_to_f16(const void *x, int dtype, int64_t rows, int64_t dim, void *out_f16,
                        float *row_scale, const float *centroids, int bits, float *table_scale_out,
                        int *zero_words, int zero_count, cudaStream_t stream);
@@ -656,8 +657,11 @@ const char *oq_linear_kernel_name(int64_t rows, int64_t in_features, int64_t out
                  ? "rotate_quantize + stream_rows_w4_kernel"
                  : "rotate_quantize + small_rows_w4_kernel";
     case OQ_KERNEL_TCGEN05:
-      return use_skinny(rows, in_features, out_features, weight_bits, dtype, mode)
-                 ? "rotate_quantize + skinny_tcgen05_kernel"
+      if (use_skinny(rows, in_features, out_features, weight_bits, dtype, mode)) {
+        return "rotate_quantize + skinny_tcgen05_kernel";
+      }
+      return tcgen05_gemm_kernel_name(rows, out_features, weight_bits)[5] == 'p'
+                 ? "rotate_quantize + gemm_pair_tcgen05_kernel"
                  : "rotate_quantize + gemm_w4_tcgen05_kernel";
     default:
       return "rotate_quantize + tiled_matmul_kernel";

@@ -57,6 +57,9 @@ constexpr int kBK = 64;
 constexpr int kEpilogueWarps = 8;  // two accumulators x four TMEM lane quarters
 constexpr float kCentroidScale = kTableScaleBase;  // table scale when none was searched
 constexpr uint32_t kSpinLimit = 1u << 22;
+// rates of the CTA-pair kernel relative to the 256-wide single-CTA tile
+constexpr double kPairRate256 = 1.10;
+constexpr double kPairRate192 = 0.98;
 
 template <int BN, int BITS>
 struct Tile {
@@ -64,18 +67,19 @@ struct Tile {
   static constexpr int kABytes = kBM * kBK * 2;        // 32 KB
   static constexpr int kBBytes = BN * kBK * 2;         // expanded f16 tile
   static constexpr int kRowBytes = kBK * BITS / 8;     // packed bytes of one weight row per k step
-  static constexpr int kPBytes = BN * kRowBytes;       // packed tile
   // 3-bit rows advance by 24 bytes per k step, which no bulk tensor copy can address
   // (16-byte rule); those tiles are read from global memory by the expanders instead.
   // (Reading 4-bit tiles the same way -- skipping the shared-memory round trip of the packed
   // bytes -- measured +1.4 % at 4608 rows with 3072-wide layers and -1.5 % at K = 12288; not
   // worth a second code path.)
-  static constexpr bool kPackedByTma = BITS != 3;
+  static constexpr bool kPackedByTma = BITS > 4 || (BN == 256 && BITS != 3);
+  static constexpr int kPBytes = kPackedByTma ? BN * kRowBytes : 0;  // packed tile
   static constexpr int kLutBytes = BITS == 6 ? 64 * 32 * 2 : (BITS == 8 ? 256 * 8 * 2 : 0);
   // every stage starts 1024-byte aligned (the 128-byte swizzle pattern repeats every 1024 bytes)
   static constexpr int kStageBytes = (kABytes + kBBytes + kPBytes + 1023) / 1024 * 1024;
+  static constexpr int kCentFloats = 1 << BITS;
   static constexpr int kHeaderBytes =
-      256 /*barriers*/ + 2 * BN * 4 /*scale,bias*/ + 256 * 4 /*centroids*/ + kLutBytes;
+      256 /*barriers*/ + 2 * BN * 4 /*scale,bias*/ + kCentFloats * 4 /*centroids*/ + kLutBytes;
   // as many stages as fit in the 227 KB a CTA may use, at most 4
   static constexpr int kFit = (232448 - kHeaderBytes - 1024) / kStageBytes;
   static constexpr int kStages = kFit > 4 ? 4 : kFit;
@@ -316,6 +320,31 @@ __device__ __forceinline__ void decode8_w4(uint32_t w, const RegTable &t, uint4 
   out = make_uint4(r[0], r[1], r[2], r[3]);
 }
 
+// 4-bit with a sign-symmetric table (entry 15 - i = -entry i, which holds for every Lloyd-Max
+// codebook): only the upper half of the table (entries 8..15, the positive values in ascending
+// order) is looked up.  Index i >= 8 selects entry i - 8 = its low three bits; index i < 8
+// selects entry 7 - i = its low three bits inverted, and sets the sign bit.
+__device__ __forceinline__ void decode8_w4_symmetric(uint32_t w, const RegTable &t, uint4 &out) {
+  const uint32_t neg = ~(w >> 3) & 0x11111111u;      // 1 per nibble whose bit 3 is clear
+  const uint32_t sel = (w ^ (neg * 7u)) & 0x77777777u;
+  uint32_t r[4];
+#pragma unroll
+  for (int h = 0; h < 2; ++h) {
+    const uint32_t s = sel >> (16 * h);
+    const uint32_t lo = __byte_perm(t.lo[2], t.lo[3], s);
+    const uint32_t hi = __byte_perm(t.hi[2], t.hi[3], s) | __byte_perm(0x00008000u, 0u, neg >> (16 * h));
+    pair_up(lo, hi, r[2 * h], r[2 * h + 1]);
+  }
+  out = make_uint4(r[0], r[1], r[2], r[3]);
+}
+
+// True when entry 15 - i of a 16-entry table is entry i with the sign bit flipped, for all i.
+__device__ __forceinline__ bool table_is_symmetric(const RegTable &t) {
+  return t.lo[0] == __byte_perm(t.lo[3], 0u, 0x0123u) && t.lo[1] == __byte_perm(t.lo[2], 0u, 0x0123u) &&
+         t.hi[0] == (__byte_perm(t.hi[3], 0u, 0x0123u) ^ 0x80808080u) &&
+         t.hi[1] == (__byte_perm(t.hi[2], 0u, 0x0123u) ^ 0x80808080u);
+}
+
 // 3-bit: 24 bits; spread each 3-bit field to its own selector nibble.
 __device__ __forceinline__ void decode8_w3(uint32_t w, const RegTable &t, uint4 &out) {
   uint32_t r[4];
@@ -372,6 +401,288 @@ __device__ __forceinline__ void group_bits(const uint32_t (&words)[NWORDS], int 
   hi = BITS > 4 ? __funnelshift_r(w1, w2, sh) : 0u;
 }
 
+// ---- expander warps ------------------------------------------------------------------------
+// Thread `et` of the expander warps turns the packed indices of weight row `n_first + et / kTpr`
+// into the 16-bit operand tile of every k step (T::kBBytes at offset T::kABytes of a stage).
+// Returns false when a wait gave up.
+template <class T, int BITS, bool SCALED>
+__device__ __forceinline__ bool expand_weight_tiles(const GemmParams &p, int64_t n_first, uint32_t stage_base,
+                                                    uint32_t bar_base, const float *s_cent,
+                                                    const uint16_t *s_lut, float table_scale,
+                                                    volatile int *s_abort, int warp, int lane) {
+  auto full_bar = [&](int s) { return bar_base + 8u * s; };
+  auto empty_bar = [&](int s) { return bar_base + 8u * (T::kStages + s); };
+  auto bready_bar = [&](int s) { return bar_base + 8u * (2 * T::kStages + s); };
+  const int64_t n0 = n_first;
+
+  constexpr int kThreadsPerRow = T::kTpr;
+  constexpr int kBytesPerThread = T::kRowBytes / kThreadsPerRow;
+  constexpr int kWords = kBytesPerThread / 4;
+  constexpr int kGroups = (kBK / 8) / kThreadsPerRow;   // 16-byte output chunks per thread
+  const int et = threadIdx.x;  // expander thread index (every expander warp owns rows)
+  const int row = et / kThreadsPerRow;
+  const int part = et % kThreadsPerRow;
+  // Register table (2-, 3-, 4-bit): entry i = f16(centroid[i] * table scale), or, SCALED,
+  // bf16(centroid[i] * row_norm) of the weight row this thread expands.
+  const int64_t table_row = n0 + et / kThreadsPerRow;
+  const float table_norm = (SCALED && table_row < p.out_features)
+                               ? __bfloat162float(p.row_norms[table_row]) : 0.0f;
+  RegTable table;
+#pragma unroll
+  for (int q = 0; q < 4; ++q) {
+    uint32_t hi = 0;
+    uint32_t lo = 0;
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      const int idx = 4 * q + e;
+      const float c = (BITS <= 4 && idx < (1 << BITS)) ? s_cent[idx] : 0.0f;
+      const uint32_t bits =
+          SCALED ? static_cast<uint32_t>(__bfloat16_as_ushort(__float2bfloat16_rn(__fmul_rn(c, table_norm))))
+                 : static_cast<uint32_t>(__half_as_ushort(__float2half_rn(c * table_scale)));
+      hi |= (bits >> 8) << (8 * e);
+      lo |= (bits & 0xffu) << (8 * e);
+    }
+    table.hi[q] = hi;
+    table.lo[q] = lo;
+  }
+  const uint16_t *lane_lut = s_lut + (BITS == 6 ? lane : (lane & 7));
+  // the symmetric decode is taken by the whole warp or not at all
+  const bool symmetric = BITS == 4 && __all_sync(0xffffffffu, table_is_symmetric(table));
+  const uint32_t row_off = (row >> 3) * 1024 + (row & 7) * 128;
+  // Shared-memory addresses of this thread's packed bytes and of the 16-byte chunks it writes,
+  // in stage 0.  The k loop below is unrolled over the stages, so a stage's offset is an
+  // immediate in every load and store and nothing is recomputed per k step.
+  const uint32_t src0 = stage_base + T::kABytes + T::kBBytes + row * T::kRowBytes + part * kBytesPerThread;
+  uint32_t dst0[kGroups];
+#pragma unroll
+  for (int c = 0; c < kGroups; ++c) {
+    dst0[c] = stage_base + T::kABytes + row_off + ((((part * kGroups + c) ^ (row & 7)) & 7) << 4);
+  }
+  // 3-bit rows come straight from global memory (8-byte loads, two k steps ahead).
+  const int64_t n_global = n0 + row;
+  const bool row_valid = n_global < p.out_features;
+  const uint8_t *grow = p.packed + n_global * (static_cast<int64_t>(p.k_iters) * T::kRowBytes) +
+                        part * kBytesPerThread;
+  uint32_t words[kWords];
+  auto load_global = [&](int it, uint32_t (&dst)[kWords]) {
+    if (kWords % 4 == 0 && row_valid && it < p.k_iters) {
+#pragma unroll
+      for (int q = 0; q < kWords / 4; ++q) {
+        const uint4 v = __ldg(reinterpret_cast<const uint4 *>(grow + static_cast<int64_t>(it) * T::kRowBytes) + q);
+        dst[4 * q] = v.x;
+        dst[4 * q + 1] = v.y;
+        dst[4 * q + 2] = v.z;
+        dst[4 * q + 3] = v.w;
+      }
+      return;
+    }
+    if (kWords % 2 == 0 && row_valid && it < p.k_iters) {
+#pragma unroll
+      for (int q = 0; q < kWords / 2; ++q) {
+        const uint2 v = __ldg(reinterpret_cast<const uint2 *>(grow + static_cast<int64_t>(it) * T::kRowBytes) + q);
+        dst[2 * q] = v.x;
+        dst[2 * q + 1] = v.y;
+      }
+      return;
+    }
+#pragma unroll
+    for (int q = 0; q < kWords; ++q) {
+      dst[q] = (row_valid && it < p.k_iters)
+                   ? __ldg(reinterpret_cast<const uint32_t *>(grow + static_cast<int64_t>(it) * T::kRowBytes) + q)
+                   : 0u;
+    }
+  };
+  bool ok = true;
+  const int expand_iters = warp < T::kExpanderWarps ? p.k_iters : 0;
+  uint32_t ahead_words[kWords];  // the k step after next: loads stay two steps ahead of their use
+  if (!T::kPackedByTma && expand_iters > 0) {
+    load_global(0, words);
+    load_global(1, ahead_words);
+  }
+  uint32_t phase = 0;
+  for (int it0 = 0; it0 < expand_iters && ok; it0 += T::kStages, phase ^= 1u) {
+#pragma unroll
+    for (int s = 0; s < T::kStages; ++s) {
+      const int it = it0 + s;
+      if (it >= expand_iters) {
+        break;
+      }
+      uint32_t next_words[kWords];
+      if (!T::kPackedByTma) {
+#pragma unroll
+        for (int q = 0; q < kWords; ++q) {
+          next_words[q] = ahead_words[q];
+        }
+        load_global(it + 2, ahead_words);
+      }
+      // Packed bytes that came by TMA: wait for them.  Packed bytes in registers: the only
+      // thing to wait for is the expanded tile of this stage being free again (the MMAs of
+      // the k step kStages earlier have read it) -- the activation tile is the MMA's concern.
+      if (!(T::kPackedByTma ? mbar_wait(full_bar(s), phase, s_abort, 4)
+                            : mbar_wait(empty_bar(s), phase ^ 1u, s_abort, 4))) {
+        ok = false;
+        break;
+      }
+      if (T::kPackedByTma) {
+        const uint32_t src = src0 + s * T::kStageBytes;
+        if (kBytesPerThread % 16 == 0) {
+#pragma unroll
+          for (int q = 0; q < kWords / 4; ++q) {
+            asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];"
+                         : "=r"(words[4 * q]), "=r"(words[4 * q + 1]), "=r"(words[4 * q + 2]),
+                           "=r"(words[4 * q + 3])
+                         : "r"(src + 16 * q)
+                         : "memory");
+          }
+        } else if (kBytesPerThread % 8 == 0) {
+#pragma unroll
+          for (int q = 0; q < kWords / 2; ++q) {
+            asm volatile("ld.shared.v2.b32 {%0, %1}, [%2];"
+                         : "=r"(words[2 * q]), "=r"(words[2 * q + 1])
+                         : "r"(src + 8 * q)
+                         : "memory");
+          }
+        } else {
+#pragma unroll
+          for (int q = 0; q < kWords; ++q) {
+            asm volatile("ld.shared.b32 %0, [%1];" : "=r"(words[q]) : "r"(src + 4 * q) : "memory");
+          }
+        }
+      }
+      // Decode every group first and store afterwards: the stores are volatile asm, which the
+      // compiler keeps in program order, and a decode-store-decode-store sequence would chain
+      // the (latency-bound) byte-permute sequences one after the other instead of overlapping
+      // them.
+      uint4 expanded[kGroups];
+      if (symmetric) {
+#pragma unroll
+        for (int c = 0; c < kGroups; ++c) {
+          uint32_t lo;
+          uint32_t hi;
+          group_bits<BITS, kWords>(words, c, lo, hi);
+          decode8_w4_symmetric(lo, table, expanded[c]);
+        }
+      } else {
+#pragma unroll
+        for (int c = 0; c < kGroups; ++c) {
+          uint32_t lo;
+          uint32_t hi;
+          group_bits<BITS, kWords>(words, c, lo, hi);
+          if (BITS == 4) {
+            decode8_w4(lo, table, expanded[c]);
+          } else if (BITS == 3) {
+            decode8_w3(lo, table, expanded[c]);
+          } else if (BITS == 2) {
+            decode8_w2(lo, table, expanded[c]);
+          } else if (BITS == 6) {
+            decode8_lut<6, 32>(lo, hi, lane_lut, expanded[c]);
+          } else {
+            decode8_lut<8, 8>(lo, hi, lane_lut, expanded[c]);
+          }
+        }
+      }
+#pragma unroll
+      for (int c = 0; c < kGroups; ++c) {
+        asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(dst0[c] + s * T::kStageBytes),
+                     "r"(expanded[c].x), "r"(expanded[c].y), "r"(expanded[c].z), "r"(expanded[c].w)
+                     : "memory");
+      }
+      if (!T::kPackedByTma) {
+#pragma unroll
+        for (int q = 0; q < kWords; ++q) {
+          words[q] = next_words[q];
+        }
+      }
+      fence_proxy_async_smem();
+      __syncwarp();
+      if (lane == 0) {
+        mbar_arrive(bready_bar(s));
+      }
+    }
+  }
+  return ok;
+}
+
+// ---- epilogue -------------------------------------------------------------------------------
+// Warp w (0..7) reads accumulator w / 4, TMEM lanes 32 * (w % 4) .., of the CTA's 256 x BN tile
+// whose first row is m0 and first column n0, and stores it to every destination buffer.
+template <class T, int BN, bool SCALED>
+__device__ __forceinline__ void store_output_tile(const GemmParams &p, int64_t m0, int64_t n0,
+                                                  uint32_t tmem_base, unsigned char *stage_ptr,
+                                                  uint32_t acc_full_bar, const float *s_scale,
+                                                  const float *s_bias, volatile int *s_abort, bool ok,
+                                                  int warp, int lane) {
+
+  // A lane of tcgen05.ld holds one output ROW, so storing from registers would write 32
+  // scattered 16-byte pieces per instruction.  The warp instead parks its 32 x BN bf16 tile
+  // in the (now idle) pipeline stages and writes it out row by row: one instruction = one
+  // contiguous run of BN*2 bytes, which is what both L2 and -- for a peer GPU's buffer --
+  // NVLink want.  The row pitch is padded by 16 bytes so that the row-per-lane writes hit
+  // all banks.
+  constexpr int kPitch = BN * 2 + 16;
+  static_assert(kEpilogueWarps * 32 * kPitch <= T::kStages * T::kStageBytes, "epilogue staging space");
+  if (ok && warp < kEpilogueWarps && mbar_wait(acc_full_bar, 0, s_abort, 5)) {
+    tc_fence_after();
+    const int half = warp >> 2;
+    const int quarter = warp & 3;
+    const int64_t m_first = m0 + half * 128 + quarter * 32;
+    const int64_t m = m_first + lane;
+    const float row_scale = m < p.rows ? (SCALED ? 1.0f : p.row_scale[m]) : 0.0f;
+    unsigned char *park = stage_ptr + warp * (32 * kPitch);
+#pragma unroll 1
+    for (int c0 = 0; c0 < BN; c0 += 32) {
+      uint32_t v[32];
+      tmem_ld_32x32b_x32(tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + half * BN + c0, v);
+      tmem_ld_wait();
+      uint4 *dst = reinterpret_cast<uint4 *>(park + lane * kPitch + c0 * 2);
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        uint32_t w[4];
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const int j = 4 * q + e;
+          const float a = fmaf(__uint_as_float(v[2 * j]), row_scale * s_scale[c0 + 2 * j],
+                               s_bias[c0 + 2 * j]);
+          const float b = fmaf(__uint_as_float(v[2 * j + 1]), row_scale * s_scale[c0 + 2 * j + 1],
+                               s_bias[c0 + 2 * j + 1]);
+          const __nv_bfloat162 h = __floats2bfloat162_rn(a, b);
+          w[e] = *reinterpret_cast<const uint32_t *>(&h);
+        }
+        dst[q] = make_uint4(w[0], w[1], w[2], w[3]);
+      }
+    }
+    __syncwarp();
+    // lane l carries columns 8l .. 8l+7 of every row
+    const bool vec_ok = (p.out_features % 8) == 0 && (p.out_ld % 8) == 0 && (p.out_col % 8) == 0;
+    const int64_t n = n0 + lane * 8;
+    const bool lane_in_tile = lane * 8 < BN;
+    const bool lane_full = lane_in_tile && n + 8 <= p.out_features;
+    const int64_t rows_here = p.rows - m_first < 32 ? p.rows - m_first : 32;
+    for (int d = 0; d < p.n_outs; ++d) {
+      __nv_bfloat16 *out = static_cast<__nv_bfloat16 *>(p.outs[d]) + p.out_col + n;
+#pragma unroll 4
+      for (int r = 0; r < rows_here; ++r) {
+        if (!lane_in_tile) {
+          continue;
+        }
+        const uint4 val = *reinterpret_cast<const uint4 *>(park + r * kPitch + lane * 16);
+        __nv_bfloat16 *dst = out + (m_first + r) * p.out_ld;
+        if (vec_ok && lane_full) {
+          *reinterpret_cast<uint4 *>(dst) = val;
+        } else {
+          const uint32_t w[4] = {val.x, val.y, val.z, val.w};
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            if (n + j < p.out_features) {
+              reinterpret_cast<uint16_t *>(dst)[j] = static_cast<uint16_t>(w[j >> 1] >> ((j & 1) * 16));
+            }
+          }
+        }
+      }
+    }
+  }
+}
+
 template <int BN, int BITS, bool SCALED = false>
 __global__ void __launch_bounds__((Tile<BN, BITS>::kThreads), 1)
 gemm_w4_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
@@ -384,8 +695,8 @@ gemm_w4_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
   volatile int *s_abort = reinterpret_cast<volatile int *>(smem_raw + 200);
   float *s_scale = reinterpret_cast<float *>(smem_raw + 256);
   float *s_bias = s_scale + BN;
-  float *s_cent = s_bias + BN;                                   // [256] codebook
-  uint16_t *s_lut = reinterpret_cast<uint16_t *>(s_cent + 256);  // 6- and 8-bit tables only
+  float *s_cent = s_bias + BN;                                   // [2^BITS] codebook
+  uint16_t *s_lut = reinterpret_cast<uint16_t *>(s_cent + T::kCentFloats);  // 6- and 8-bit tables only
   const uint32_t header_end = smem_u32(smem_raw) + T::kHeaderBytes;
   const uint32_t stage_base = (header_end + 1023u) & ~1023u;
   unsigned char *stage_ptr = smem_raw + (stage_base - smem_u32(smem_raw));
@@ -509,223 +820,11 @@ gemm_w4_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
       }
     }
   } else {
-    // ---- expanders ----
-    constexpr int kThreadsPerRow = T::kTpr;
-    constexpr int kBytesPerThread = T::kRowBytes / kThreadsPerRow;
-    constexpr int kWords = kBytesPerThread / 4;
-    constexpr int kGroups = (kBK / 8) / kThreadsPerRow;   // 16-byte output chunks per thread
-    const int et = threadIdx.x;  // expander thread index (every expander warp owns rows)
-    const int row = et / kThreadsPerRow;
-    const int part = et % kThreadsPerRow;
-    // Register table (2-, 3-, 4-bit): entry i = f16(centroid[i] * table scale), or, SCALED,
-    // bf16(centroid[i] * row_norm) of the weight row this thread expands.
-    const int64_t table_row = n0 + et / kThreadsPerRow;
-    const float table_norm = (SCALED && table_row < p.out_features)
-                                 ? __bfloat162float(p.row_norms[table_row]) : 0.0f;
-    RegTable table;
-#pragma unroll
-    for (int q = 0; q < 4; ++q) {
-      uint32_t hi = 0;
-      uint32_t lo = 0;
-#pragma unroll
-      for (int e = 0; e < 4; ++e) {
-        const int idx = 4 * q + e;
-        const float c = (BITS <= 4 && idx < (1 << BITS)) ? s_cent[idx] : 0.0f;
-        const uint32_t bits =
-            SCALED ? static_cast<uint32_t>(__bfloat16_as_ushort(__float2bfloat16_rn(__fmul_rn(c, table_norm))))
-                   : static_cast<uint32_t>(__half_as_ushort(__float2half_rn(c * table_scale)));
-        hi |= (bits >> 8) << (8 * e);
-        lo |= (bits & 0xffu) << (8 * e);
-      }
-      table.hi[q] = hi;
-      table.lo[q] = lo;
-    }
-    const uint16_t *lane_lut = s_lut + (BITS == 6 ? lane : (lane & 7));
-    const uint32_t row_off = (row >> 3) * 1024 + (row & 7) * 128;
-    // 3-bit rows come straight from global memory (8-byte loads, one k step ahead).
-    const int64_t n_global = n0 + row;
-    const bool row_valid = n_global < p.out_features;
-    const uint8_t *grow = p.packed + n_global * (static_cast<int64_t>(p.k_iters) * T::kRowBytes) +
-                          part * kBytesPerThread;
-    uint32_t words[kWords];
-    auto load_global = [&](int it, uint32_t (&dst)[kWords]) {
-      if (kWords % 4 == 0 && row_valid && it < p.k_iters) {
-#pragma unroll
-        for (int q = 0; q < kWords / 4; ++q) {
-          const uint4 v = __ldg(reinterpret_cast<const uint4 *>(grow + static_cast<int64_t>(it) * T::kRowBytes) + q);
-          dst[4 * q] = v.x;
-          dst[4 * q + 1] = v.y;
-          dst[4 * q + 2] = v.z;
-          dst[4 * q + 3] = v.w;
-        }
-        return;
-      }
-#pragma unroll
-      for (int q = 0; q < kWords; ++q) {
-        dst[q] = (row_valid && it < p.k_iters)
-                     ? __ldg(reinterpret_cast<const uint32_t *>(grow + static_cast<int64_t>(it) * T::kRowBytes) + q)
-                     : 0u;
-      }
-    };
-    bool ok = true;
-    const int expand_iters = warp < T::kExpanderWarps ? p.k_iters : 0;
-    uint32_t ahead_words[kWords];  // the k step after next: loads stay two steps ahead of their use
-    if (!T::kPackedByTma && expand_iters > 0) {
-      load_global(0, words);
-      load_global(1, ahead_words);
-    }
-    for (int it = 0; it < expand_iters; ++it) {
-      const int s = it % T::kStages;
-      const uint32_t phase = (it / T::kStages) & 1u;
-      uint32_t next_words[kWords];
-      if (!T::kPackedByTma) {
-#pragma unroll
-        for (int q = 0; q < kWords; ++q) {
-          next_words[q] = ahead_words[q];
-        }
-        load_global(it + 2, ahead_words);
-      }
-      if (!mbar_wait(full_bar(s), phase, s_abort, 4)) {
-        ok = false;
-        break;
-      }
-      if (T::kPackedByTma) {
-        const unsigned char *src = p_ptr(s) + row * T::kRowBytes + part * kBytesPerThread;
-        if (kBytesPerThread % 16 == 0) {
-#pragma unroll
-          for (int q = 0; q < kWords / 4; ++q) {
-            const uint4 v = reinterpret_cast<const uint4 *>(src)[q];
-            words[4 * q + 0] = v.x;
-            words[4 * q + 1] = v.y;
-            words[4 * q + 2] = v.z;
-            words[4 * q + 3] = v.w;
-          }
-        } else if (kBytesPerThread % 8 == 0) {
-#pragma unroll
-          for (int q = 0; q < kWords / 2; ++q) {
-            const uint2 v = reinterpret_cast<const uint2 *>(src)[q];
-            words[2 * q] = v.x;
-            words[2 * q + 1] = v.y;
-          }
-        } else {
-#pragma unroll
-          for (int q = 0; q < kWords; ++q) {
-            words[q] = reinterpret_cast<const uint32_t *>(src)[q];
-          }
-        }
-      }
-      const uint32_t dst_row = b_addr(s) + row_off;
-      // Decode every group first and store afterwards: the stores are volatile asm, which the
-      // compiler keeps in program order, and a decode-store-decode-store sequence would chain
-      // the (latency-bound) byte-permute sequences one after the other instead of overlapping them.
-      uint4 expanded[kGroups];
-#pragma unroll
-      for (int c = 0; c < kGroups; ++c) {
-        uint32_t lo;
-        uint32_t hi;
-        group_bits<BITS, kWords>(words, c, lo, hi);
-        if (BITS == 4) {
-          decode8_w4(lo, table, expanded[c]);
-        } else if (BITS == 3) {
-          decode8_w3(lo, table, expanded[c]);
-        } else if (BITS == 2) {
-          decode8_w2(lo, table, expanded[c]);
-        } else if (BITS == 6) {
-          decode8_lut<6, 32>(lo, hi, lane_lut, expanded[c]);
-        } else {
-          decode8_lut<8, 8>(lo, hi, lane_lut, expanded[c]);
-        }
-      }
-#pragma unroll
-      for (int c = 0; c < kGroups; ++c) {
-        const int chunk = part * kGroups + c;
-        const uint32_t dst = dst_row + (((chunk ^ (row & 7)) & 7) << 4);
-        asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(dst), "r"(expanded[c].x),
-                     "r"(expanded[c].y), "r"(expanded[c].z), "r"(expanded[c].w)
-                     : "memory");
-      }
-      if (!T::kPackedByTma) {
-#pragma unroll
-        for (int q = 0; q < kWords; ++q) {
-          words[q] = next_words[q];
-        }
-      }
-      fence_proxy_async_smem();
-      __syncwarp();
-      if (lane == 0) {
-        mbar_arrive(bready_bar(s));
-      }
-    }
-
-    // ---- epilogue: warp w reads accumulator w/4, TMEM lanes 32*(w%4).. ----
-    // A lane of tcgen05.ld holds one output ROW, so storing from registers would write 32
-    // scattered 16-byte pieces per instruction.  The warp instead parks its 32 x BN bf16 tile
-    // in the (now idle) pipeline stages and writes it out row by row: one instruction = one
-    // contiguous run of BN*2 bytes, which is what both L2 and -- for a peer GPU's buffer --
-    // NVLink want.  The row pitch is padded by 16 bytes so that the row-per-lane writes hit
-    // all banks.
-    constexpr int kPitch = BN * 2 + 16;
-    static_assert(kEpilogueWarps * 32 * kPitch <= T::kStages * T::kStageBytes, "epilogue staging space");
-    if (ok && warp < kEpilogueWarps && mbar_wait(acc_full_bar, 0, s_abort, 5)) {
-      tc_fence_after();
-      const int half = warp >> 2;
-      const int quarter = warp & 3;
-      const int64_t m_first = m0 + half * 128 + quarter * 32;
-      const int64_t m = m_first + lane;
-      const float row_scale = m < p.rows ? (SCALED ? 1.0f : p.row_scale[m]) : 0.0f;
-      unsigned char *park = stage_ptr + warp * (32 * kPitch);
-#pragma unroll 1
-      for (int c0 = 0; c0 < BN; c0 += 32) {
-        uint32_t v[32];
-        tmem_ld_32x32b_x32(tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + half * BN + c0, v);
-        tmem_ld_wait();
-        uint4 *dst = reinterpret_cast<uint4 *>(park + lane * kPitch + c0 * 2);
-#pragma unroll
-        for (int q = 0; q < 4; ++q) {
-          uint32_t w[4];
-#pragma unroll
-          for (int e = 0; e < 4; ++e) {
-            const int j = 4 * q + e;
-            const float a = fmaf(__uint_as_float(v[2 * j]), row_scale * s_scale[c0 + 2 * j],
-                                 s_bias[c0 + 2 * j]);
-            const float b = fmaf(__uint_as_float(v[2 * j + 1]), row_scale * s_scale[c0 + 2 * j + 1],
-                                 s_bias[c0 + 2 * j + 1]);
-            const __nv_bfloat162 h = __floats2bfloat162_rn(a, b);
-            w[e] = *reinterpret_cast<const uint32_t *>(&h);
-          }
-          dst[q] = make_uint4(w[0], w[1], w[2], w[3]);
-        }
-      }
-      __syncwarp();
-      // lane l carries columns 8l .. 8l+7 of every row
-      const bool vec_ok = (p.out_features % 8) == 0 && (p.out_ld % 8) == 0 && (p.out_col % 8) == 0;
-      const int64_t n = n0 + lane * 8;
-      const bool lane_in_tile = lane * 8 < BN;
-      const bool lane_full = lane_in_tile && n + 8 <= p.out_features;
-      const int64_t rows_here = p.rows - m_first < 32 ? p.rows - m_first : 32;
-      for (int d = 0; d < p.n_outs; ++d) {
-        __nv_bfloat16 *out = static_cast<__nv_bfloat16 *>(p.outs[d]) + p.out_col + n;
-#pragma unroll 4
-        for (int r = 0; r < rows_here; ++r) {
-          if (!lane_in_tile) {
-            continue;
-          }
-          const uint4 val = *reinterpret_cast<const uint4 *>(park + r * kPitch + lane * 16);
-          __nv_bfloat16 *dst = out + (m_first + r) * p.out_ld;
-          if (vec_ok && lane_full) {
-            *reinterpret_cast<uint4 *>(dst) = val;
-          } else {
-            const uint32_t w[4] = {val.x, val.y, val.z, val.w};
-#pragma unroll
-            for (int j = 0; j < 8; ++j) {
-              if (n + j < p.out_features) {
-                reinterpret_cast<uint16_t *>(dst)[j] = static_cast<uint16_t>(w[j >> 1] >> ((j & 1) * 16));
-              }
-            }
-          }
-        }
-      }
-    }
+    // ---- expanders, then epilogue ----
+    const bool ok = expand_weight_tiles<T, BITS, SCALED>(p, n0, stage_base, bar_base, s_cent, s_lut,
+                                                         table_scale, s_abort, warp, lane);
+    store_output_tile<T, BN, SCALED>(p, m0, n0, tmem_base, stage_ptr, acc_full_bar, s_scale, s_bias,
+                                     s_abort, ok, warp, lane);
   }
 
   tc_fence_before();
@@ -856,6 +955,7 @@ int launch_bn(const CUtensorMap &map_a, const CUtensorMap &map_p, const GemmPara
   return OQ_OK;
 }
 
+#include "gemm_pair_tcgen05.cuh"
 #include "skinny_tcgen05.cuh"
 
 }  // namespace
@@ -901,6 +1001,75 @@ int launch_bits(int bn, const CUtensorMap &map_a, const CUtensorMap &map_p, cons
   }
 }
 
+// Output tile of the large-row kernel for a problem: `*tile_n` = width of the single-CTA tile
+// (256 | 192 | 128), `*pair_n` = width of the CTA-pair tile (256 | 192) or 0 when the single-CTA
+// kernel runs.
+void choose_tile(int64_t rows, int64_t out_features, int bits, int sm_count, int *tile_n, int *pair_n) {
+  // Tile width.  Wider tiles move fewer shared-memory bytes per flop (the activation tile
+  // is re-read once per MMA), narrower ones can fill the last wave better; pick the width
+  // with the best product of the two.  The per-width rates are measured ratios.
+  const int64_t m_tiles = (rows + kBM - 1) / kBM;
+  auto score = [&](int width, double rate) {
+    const int64_t tiles = m_tiles * ((out_features + width - 1) / width);
+    const int64_t waves = (tiles + sm_count - 1) / sm_count;
+    const double useful = static_cast<double>(out_features) /
+                          static_cast<double>(((out_features + width - 1) / width) * width);
+    return rate * useful * static_cast<double>(tiles) / static_cast<double>(waves * sm_count);
+  };
+  // 6- and 8-bit packed tiles leave room for only two 256-wide stages; start from 192 there.
+  int bn = bits >= 6 ? 192 : 256;
+  double best = bits >= 6 ? score(192, 0.93) : score(256, 1.0);
+  if (score(192, 0.93) > best) {
+    bn = 192;
+    best = score(192, 0.93);
+  }
+  if (score(128, 0.76) > best) {
+    bn = 128;
+  }
+  // the tile_n tunable (128 | 192 | 256) pins the width (tests and profiling)
+  {
+    const int value = tunable(OQ_TUNE_TILE_N);
+    if (value == 128 || value == 192 || value == 256) {
+      bn = value;
+    }
+  }
+  // A pair of CTAs (cta_group::2) on a 512 x 256 (or 512 x 192) tile halves the decode work
+  // and the shared-memory traffic per MMA; it wins when its grid fills the machine about as
+  // well.  The pair tunable pins the choice: 0 = never, 1 = best pair width, 192 / 256 = that
+  // pair width.
+  const int64_t m_pairs = (rows + 2 * kBM - 1) / (2 * kBM);
+  int pair_bn = 0;
+  if (bits <= 4) {
+    auto pair_score = [&](int width, double rate) {
+      const int64_t n_tiles_w = (out_features + width - 1) / width;
+      const int64_t ctas = 2 * m_pairs * n_tiles_w;
+      const int64_t waves = (ctas + sm_count - 1) / sm_count;
+      const double useful_n = static_cast<double>(out_features) / static_cast<double>(n_tiles_w * width);
+      const double useful_m = static_cast<double>(rows) / static_cast<double>(m_pairs * 2 * kBM);
+      return rate * useful_n * useful_m * static_cast<double>(ctas) / static_cast<double>(waves * sm_count);
+    };
+    const double single_useful_m = static_cast<double>(rows) / static_cast<double>(m_tiles * kBM);
+    const double single_score =
+        score(bn, bn == 256 ? 1.0 : (bn == 192 ? 0.93 : 0.76)) * single_useful_m;
+    const double p256 = pair_score(256, kPairRate256);
+    const double p192 = pair_score(192, kPairRate192);
+    const int best_pair = p192 > p256 ? 192 : 256;
+    if (std::max(p256, p192) > single_score) {
+      pair_bn = best_pair;
+    }
+    const int forced = tunable(OQ_TUNE_PAIR);
+    if (forced == 0) {
+      pair_bn = 0;
+    } else if (forced == 192 || forced == 256) {
+      pair_bn = forced;
+    } else if (forced > 0) {
+      pair_bn = best_pair;
+    }
+  }
+  *tile_n = bn;
+  *pair_n = pair_bn;
+}
+
 int launch_tcgen05_gemm_scatter(void *const *outs, int n_outs, int64_t out_ld, int64_t out_col,
                                 const void *x, const float *row_scale, const float *table_scale,
                                 int64_t rows, int64_t in_features, int64_t out_features,
@@ -942,36 +1111,19 @@ int launch_tcgen05_gemm_scatter(void *const *outs, int n_outs, int64_t out_ld, i
   OQ_CHECK_CUDA(cudaGetDevice(&device));
   OQ_CHECK_CUDA(cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, device));
 
-  // Tile width.  Wider tiles move fewer shared-memory bytes per flop (the activation tile
-  // is re-read once per MMA), narrower ones can fill the last wave better; pick the width
-  // with the best product of the two.  The per-width rates are measured ratios.
+  int bn = 0;
+  int pair_bn = 0;
+  choose_tile(rows, out_features, bits, sm_count, &bn, &pair_bn);
   const int64_t m_tiles = (rows + kBM - 1) / kBM;
-  auto score = [&](int width, double rate) {
-    const int64_t tiles = m_tiles * ((out_features + width - 1) / width);
-    const int64_t waves = (tiles + sm_count - 1) / sm_count;
-    const double useful = static_cast<double>(out_features) /
-                          static_cast<double>(((out_features + width - 1) / width) * width);
-    return rate * useful * static_cast<double>(tiles) / static_cast<double>(waves * sm_count);
-  };
-  // 6- and 8-bit packed tiles leave room for only two 256-wide stages; start from 192 there.
-  int bn = bits >= 6 ? 192 : 256;
-  double best = bits >= 6 ? score(192, 0.93) : score(256, 1.0);
-  if (score(192, 0.93) > best) {
-    bn = 192;
-    best = score(192, 0.93);
-  }
-  if (score(128, 0.76) > best) {
-    bn = 128;
-  }
-  // the tile_n tunable (128 | 192 | 256) pins the width (tests and profiling)
-  {
-    const int value = tunable(OQ_TUNE_TILE_N);
-    if (value == 128 || value == 192 || value == 256) {
-      bn = value;
-    }
+  const int64_t m_pairs = (rows + 2 * kBM - 1) / (2 * kBM);
+  const bool use_pair = pair_bn != 0;
+  const int64_t pair_n_tiles = use_pair ? (out_features + pair_bn - 1) / pair_bn : 0;
+  const int64_t pair_tiles = m_pairs * pair_n_tiles;
+  if (use_pair) {
+    bn = pair_bn / 2;  // the packed tensor map's box: the weight rows one CTA of the pair expands
   }
   const int64_t n_tiles = (out_features + bn - 1) / bn;
-  OQ_CHECK_ARG(m_tiles * n_tiles < (1ll << 31), "too many output tiles");
+  OQ_CHECK_ARG(m_tiles * n_tiles < (1ll << 31) && pair_tiles < (1ll << 30), "too many output tiles");
 
   CUtensorMap map_a;
   CUtensorMap map_p;
@@ -1036,6 +1188,23 @@ int launch_tcgen05_gemm_scatter(void *const *outs, int n_outs, int64_t out_ld, i
   if (tunable(OQ_TUNE_TILE_ORDER) >= 0) {  // 0 / 1 pins it (profiling)
     p.columns_fastest = tunable(OQ_TUNE_TILE_ORDER) != 0 ? 1 : 0;
   }
+  if (use_pair) {
+    p.m_tiles = static_cast<int>(m_pairs);
+    p.n_tiles = static_cast<int>(pair_n_tiles);
+    const int pairs = static_cast<int>(pair_tiles);
+    if (scaled) {
+      switch (bits) {
+        case 2: return launch_pair_bits<2, true>(pair_bn, map_a, map_p, p, pairs, stream);
+        case 3: return launch_pair_bits<3, true>(pair_bn, map_a, map_p, p, pairs, stream);
+        default: return launch_pair_bits<4, true>(pair_bn, map_a, map_p, p, pairs, stream);
+      }
+    }
+    switch (bits) {
+      case 2: return launch_pair_bits<2, false>(pair_bn, map_a, map_p, p, pairs, stream);
+      case 3: return launch_pair_bits<3, false>(pair_bn, map_a, map_p, p, pairs, stream);
+      default: return launch_pair_bits<4, false>(pair_bn, map_a, map_p, p, pairs, stream);
+    }
+  }
   const int grid = static_cast<int>(m_tiles * n_tiles);
   if (scaled) {
     switch (bits) {
@@ -1051,6 +1220,20 @@ int launch_tcgen05_gemm_scatter(void *const *outs, int n_outs, int64_t out_ld, i
     case 6: return launch_bits<6>(bn, map_a, map_p, p, grid, stream);
     default: return launch_bits<8>(bn, map_a, map_p, p, grid, stream);
   }
+}
+
+// Name of the large-row kernel this problem gets (for reports; launches nothing).
+const char *tcgen05_gemm_kernel_name(int64_t rows, int64_t out_features, int bits) {
+  int device = 0;
+  int sm_count = 0;
+  if (cudaGetDevice(&device) != cudaSuccess ||
+      cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, device) != cudaSuccess || sm_count <= 0) {
+    sm_count = 148;
+  }
+  int bn = 0;
+  int pair_bn = 0;
+  choose_tile(rows, out_features, bits, sm_count, &bn, &pair_bn);
+  return pair_bn != 0 ? "gemm_pair_tcgen05_kernel" : "gemm_w4_tcgen05_kernel";
 }
 
 // Few tokens (rows <= 128): the operand-swapped kernel of skinny_tcgen05.cuh.

@@ -211,3 +211,54 @@ def test_tcgen05_bf16_scaled_operand(oracle, bits, rows, k, n):
                                mode=oracle.MM_BF16_LUT)
     _check_close(y, ref, ("bf16_scaled", bits, rows, k, n))
     assert rel_l2(y.float().cpu(), ref[0].float()) < 3e-4
+
+
+@pytest.mark.parametrize("pair_width", [192, 256])
+@pytest.mark.parametrize("bits,scaled", [(4, False), (3, False), (2, False), (4, True), (3, True)])
+def test_tcgen05_cta_pair_kernel(oracle, pair_width, bits, scaled, tunables):
+    """The cta_group::2 variant (two CTAs share every expanded weight tile): against the oracle
+    on a shape that is ragged in M (the pair's second CTA is partly, then wholly, out of range)
+    and in N, and bit for bit against the single-CTA kernel -- both accumulate the same products
+    in the same order."""
+    dev = _dev()
+    rows, k, n = 1100, 768, 840
+    idx, packed, rn, bias = _random_layer(k, n, bits, seed=bits * 5 + pair_width)
+    cent = get_codebook(k, bits).centroids
+    x = (torch.randn(rows, k) * 0.8).to(torch.bfloat16)
+    mode = native.WEIGHT_BF16_SCALED if scaled else native.WEIGHT_CENTROID
+    kw = dict(bits=bits, out_features=n, in_features=k, bias=bias, kernel=native.KERNEL_TCGEN05,
+              weight_mode=mode)
+    native.gemm_clear_device_status()
+    tunables.set("pair", 0)
+    single = native.matmul_packed_weight(x.to(dev), packed.to(dev), rn, cent, **kw)
+    tunables.set("pair", pair_width)
+    launches = native.launch_count()
+    paired = native.matmul_packed_weight(x.to(dev), packed.to(dev), rn, cent, **kw)
+    assert native.launch_count() > launches
+    _assert_status_clean()
+    assert torch.equal(single, paired)
+    ref = oracle.matmul_packed(x, packed, rn, cent, bits=bits, out_features=n, bias=bias,
+                               mode=oracle.MM_BF16_LUT if scaled else oracle.MM_FP32_CENTROIDS)
+    _check_close(paired, ref, ("pair", pair_width, bits, scaled))
+
+
+@pytest.mark.parametrize("pair", [0, 256])
+def test_tcgen05_table_without_sign_symmetry(oracle, pair, tunables):
+    """Lloyd-Max tables are sign-symmetric and take the short 4-bit decode; any other table
+    must take the general one and give the same kind of answer."""
+    dev = _dev()
+    rows, k, n = 600, 512, 520
+    idx, packed, rn, bias = _random_layer(k, n, 4, seed=77)
+    cent = get_codebook(k, 4).centroids.clone()
+    cent[3] *= 1.07              # breaks entry 3 = -entry 12
+    cent = torch.sort(cent).values
+    assert not torch.equal(cent, -cent.flip(0))
+    x = (torch.randn(rows, k) * 0.8).to(torch.bfloat16)
+    tunables.set("pair", pair)
+    native.gemm_clear_device_status()
+    y = native.matmul_packed_weight(x.to(dev), packed.to(dev), rn, cent, bits=4, out_features=n,
+                                    in_features=k, bias=bias, kernel=native.KERNEL_TCGEN05)
+    _assert_status_clean()
+    ref = oracle.matmul_packed(x, packed, rn, cent, bits=4, out_features=n, bias=bias,
+                               mode=oracle.MM_FP32_CENTROIDS)
+    _check_close(y, ref, ("asymmetric table", pair))
