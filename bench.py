@@ -61,7 +61,7 @@ WORKLOAD_NAMES = ("dit_block", "single_layer", "mixed_bit", "video_dit", "vit_de
 
 # DRAM bytes (read + write) per launch of the dominant kernel from an ncu capture of the
 # one-GPU run, keyed by workload (None until captured).
-NCU_TRAFFIC_BYTES = {"dit_block": 97.5e6}
+NCU_TRAFFIC_BYTES = {"dit_block": 100.8e6}
 
 
 def mixed_bit_assignment(blocks: int = 8, protected_blocks: int = 4):

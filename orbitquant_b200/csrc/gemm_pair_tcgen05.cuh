@@ -16,12 +16,12 @@
 //                        tile -> local `full[s]`; its expanders write its half of the weight
 //                        tile and arrive on the local `bready[s]`.
 //   hand-over            the peer CTA's otherwise idle MMA-warp thread waits for the peer's
-//                        `full[s]` and `bready[s]` and forwards ONE arrival (release at cluster
-//                        scope) to `peer[s]` in the leader.  A cluster-scope release costs a
-//                        memory barrier of about a microsecond; issued by every expander warp
-//                        (sixteen per k step) it was what made an earlier pair kernel slower
-//                        than the single-CTA one, issued once per k step by a thread with
-//                        nothing else to do it runs beside the pipeline.
+//                        `full[s]` and `bready[s]` and forwards ONE arrival to `peer[s]` in the
+//                        leader, released at CTA scope (see mbar_arrive_remote).  A
+//                        cluster-scope release from every expander warp instead (sixteen per k
+//                        step) stalls the expanders on a memory barrier of about a microsecond
+//                        each time: measured 4 stall cycles per issued instruction and a
+//                        tensor pipe 50 % busy, slower than one CTA.
 //   MMA                  the leader waits for its `full[s]`, `bready[s]` and `peer[s]`, issues
 //                        2 x 4 MMAs, and one tcgen05.commit arrives on both CTAs' `empty[s]`
 //                        (and, at the end, `acc_full`).
@@ -254,7 +254,7 @@ gemm_pair_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
       }
     } else if (lane == 0) {
       // The peer's hand-over thread: its activation tile has landed and its half of the weight
-      // tile is written -> one arrival, released at cluster scope, in the leader.
+      // tile is written -> one arrival in the leader.
       const uint32_t leader_peer0 = map_to_cta(peer_bar(0), 0);
       for (int it = 0; it < p.k_iters; ++it) {
         const int s = it % T::kStages;
