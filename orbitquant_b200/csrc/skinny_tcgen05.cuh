@@ -383,6 +383,9 @@ skinny_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x,
       }
     };
     const uint16_t *lane_lut = s_lut + (BITS == 6 ? lane : (lane & 7));
+    // sign-symmetric 4-bit tables (every Lloyd-Max codebook; not the RTN integers) take the
+    // shorter decode, the whole warp or none of it
+    const bool symmetric = BITS == 4 && !RTN && __all_sync(0xffffffffu, table_is_symmetric(table));
     const uint32_t row_off = (row >> 3) * 1024 + (row & 7) * 128;
     SkinnyRing copy;
     SkinnyRing slot;
@@ -464,7 +467,9 @@ skinny_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x,
           uint32_t lo;
           uint32_t hi;
           group_bits<BITS, kWords>(words, c, lo, hi);
-          if (BITS == 4) {
+          if (symmetric) {
+            decode8_w4_symmetric(lo, table, expanded[c]);
+          } else if (BITS == 4) {
             decode8_w4(lo, table, expanded[c]);
           } else if (BITS == 3) {
             decode8_w3(lo, table, expanded[c]);
