@@ -186,7 +186,8 @@ gemm_pair_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
   tc_fence_before();
   cluster_sync_all();
   tc_fence_after();
-  asm volatile("griddepcontrol.wait;" ::: "memory");  // see the single-CTA kernel
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");  // see the single-CTA kernel
+  asm volatile("griddepcontrol.wait;" ::: "memory");
   const float table_scale =
       SCALED ? 1.0f : (p.table_scale != nullptr ? __ldg(p.table_scale) : kCentroidScale);
   for (int i = threadIdx.x; i < BN; i += T::kThreads) {

@@ -740,7 +740,10 @@ gemm_w4_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
   }
   __syncthreads();
   // The launch allows this grid to become resident while the kernel before it in the stream
-  // (the prologue) is still running; everything below reads that kernel's output.
+  // (the prologue) is still running; everything below reads that kernel's output.  The kernel
+  // after this one (the next layer's prologue, launched the same way) may in turn take over SMs
+  // as this grid's last wave drains; it touches nothing of ours before its own wait.
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   asm volatile("griddepcontrol.wait;" ::: "memory");
   // chosen by the kernel that ran just before this one (table_scale.cuh); 2^8 without it
   const float table_scale =

@@ -453,14 +453,14 @@ rotate_quantize_kernel(const PrologueParams p) {
 namespace oq {
 namespace {
 
-template <bool F16OP>
+template <bool F16OP, int TW>
 void (*warp_kernel_for(int bits))(WarpPrologueParams) {
   switch (bits) {
-    case 2: return rotate_quantize_warp_kernel<2, F16OP>;
-    case 3: return rotate_quantize_warp_kernel<3, F16OP>;
-    case 4: return rotate_quantize_warp_kernel<4, F16OP>;
-    case 6: return rotate_quantize_warp_kernel<6, F16OP>;
-    case 8: return rotate_quantize_warp_kernel<8, F16OP>;
+    case 2: return rotate_quantize_warp_kernel<2, F16OP, TW>;
+    case 3: return rotate_quantize_warp_kernel<3, F16OP, TW>;
+    case 4: return rotate_quantize_warp_kernel<4, F16OP, TW>;
+    case 6: return rotate_quantize_warp_kernel<6, F16OP, TW>;
+    case 8: return rotate_quantize_warp_kernel<8, F16OP, TW>;
     default: return nullptr;
   }
 }
@@ -470,8 +470,26 @@ void (*warp_kernel_for(int bits))(WarpPrologueParams) {
 // must run ahead of the norm warps, which run ahead of the transform warps), then as many
 // tokens per batch as fit.
 bool plan_warp_prologue(int dim, int block, int bits, int64_t rows, int max_smem, int *batch_rows,
-                        int *slots, int *ctas_per_sm, int *smem) {
+                        int *slots, int *ctas_per_sm, int *smem, int *transform_warps) {
   const int shared_per_sm = 228 * 1024;
+  // Blocks of 4096 are shared by teams of four warps and their rows leave room for one CTA per
+  // SM only: sixteen transform warps (four teams) keep that SM busy where eight leave it half
+  // idle.
+  if (block == 4 * kPwChunk) {
+    static const int kWide[][2] = {{1, 3}, {1, 2}};
+    for (const auto &choice : kWide) {
+      const int total = pw_layout(dim, block, choice[0], choice[1], bits, kPwWideWarps).total;
+      if (total <= max_smem && total + 1024 <= shared_per_sm) {
+        *batch_rows = choice[0];
+        *slots = choice[1];
+        *ctas_per_sm = 1;
+        *smem = total;
+        *transform_warps = kPwWideWarps;
+        return true;
+      }
+    }
+  }
+  *transform_warps = kPwWarps;
   static const int kChoices[][2] = {{4, 3}, {2, 4}, {2, 3}, {1, 4}, {1, 3}, {1, 2}};
   for (int per_sm = 2; per_sm >= 1; --per_sm) {
     for (const auto &choice : kChoices) {
@@ -559,8 +577,9 @@ int launch_rotate_quantize(const void *x, int x_dtype, int64_t rows, int64_t dim
     int slots = 0;
     int ctas_per_sm = 0;
     int smem_bytes = 0;
+    int transform_warps = kPwWarps;
     if (plan_warp_prologue(static_cast<int>(dim), static_cast<int>(block), bits, rows, max_smem,
-                           &batch_rows, &slots, &ctas_per_sm, &smem_bytes)) {
+                           &batch_rows, &slots, &ctas_per_sm, &smem_bytes, &transform_warps)) {
       WarpPrologueParams wp{};
       wp.x = static_cast<const uint16_t *>(x);
       wp.xq = static_cast<uint16_t *>(x_q);
@@ -584,14 +603,30 @@ int launch_rotate_quantize(const void *x, int x_dtype, int64_t rows, int64_t dim
       wp.table_scale_out = table_scale_out;
       wp.zero_words = zero_words;
       wp.zero_count = zero_words != nullptr ? zero_count : 0;
+      const bool wide = transform_warps == kPwWideWarps;
       void (*wkernel)(WarpPrologueParams) =
-          f16_row_scale != nullptr ? warp_kernel_for<true>(bits) : warp_kernel_for<false>(bits);
+          f16_row_scale != nullptr
+              ? (wide ? warp_kernel_for<true, kPwWideWarps>(bits) : warp_kernel_for<true, kPwWarps>(bits))
+              : (wide ? warp_kernel_for<false, kPwWideWarps>(bits) : warp_kernel_for<false, kPwWarps>(bits));
       OQ_CHECK_CUDA(cudaFuncSetAttribute(wkernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes));
       const int64_t batches = (rows + batch_rows - 1) / batch_rows;
       const int wgrid = static_cast<int>(std::min<int64_t>(batches, static_cast<int64_t>(sm_count) * ctas_per_sm)) +
                         (table_scale_out != nullptr ? 1 : 0);
-      wkernel<<<wgrid, kPwThreads, smem_bytes, stream>>>(wp);
-      OQ_CHECK_CUDA(cudaGetLastError());
+      // Programmatic stream serialization: the CTAs may become resident, and build their
+      // permutation and cell tables, while the kernel before this one in the stream drains its
+      // last wave; griddepcontrol.wait inside the kernel precedes every access to x, to the
+      // outputs and to the workspace.
+      cudaLaunchConfig_t config = {};
+      config.gridDim = dim3(static_cast<unsigned>(wgrid));
+      config.blockDim = dim3(static_cast<unsigned>(pw_threads(transform_warps)));
+      config.dynamicSmemBytes = static_cast<size_t>(smem_bytes);
+      config.stream = stream;
+      cudaLaunchAttribute attr[1];
+      attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+      attr[0].val.programmaticStreamSerializationAllowed = 1;
+      config.attrs = attr;
+      config.numAttrs = 1;
+      OQ_CHECK_CUDA(cudaLaunchKernelEx(&config, wkernel, wp));
       count_launch();
       return OQ_OK;
     }

@@ -45,9 +45,12 @@ __device__ int g_prologue_status = 0;  // 0 = ok; otherwise the code of the firs
 
 namespace {
 
-constexpr int kPwWarps = 8;                       // transform warps
+constexpr int kPwWarps = 8;                       // transform warps (16 in the wide variant)
+constexpr int kPwWideWarps = 16;
 constexpr int kPwNormWarps = 2;
-constexpr int kPwThreads = (kPwWarps + kPwNormWarps) * 32;
+__host__ __device__ constexpr int pw_threads(int transform_warps) {
+  return (transform_warps + kPwNormWarps) * 32;
+}
 constexpr int kPwChunk = 1024;
 constexpr int kPwRowPad = 32;                     // bytes between the rows of a slot
 constexpr int kPwMaxRows = 4;                     // tokens per batch
@@ -86,7 +89,8 @@ struct PwLayout {
   int row_pitch, slot_bytes, team_bytes, total;
 };
 
-__host__ __device__ inline PwLayout pw_layout(int dim, int block, int batch_rows, int slots, int bits) {
+__host__ __device__ inline PwLayout pw_layout(int dim, int block, int batch_rows, int slots, int bits,
+                                              int transform_warps = kPwWarps) {
   PwLayout l;
   const int cells = pw_max_cells(bits);
   int at = 128;  // barriers, counters and flags
@@ -105,7 +109,7 @@ __host__ __device__ inline PwLayout pw_layout(int dim, int block, int batch_rows
   at = (at + 127) / 128 * 128;
   const int team = block > kPwChunk ? block / kPwChunk : 1;
   l.team_bytes = team * kPwChunk * 6;                                  // fp32 scratch + 16-bit results
-  l.work = at;       at += (kPwWarps / team) * l.team_bytes;
+  l.work = at;       at += (transform_warps / team) * l.team_bytes;
   l.total = at + 128;                                                  // alignment slack
   return l;
 }
@@ -392,9 +396,11 @@ __device__ __forceinline__ void pw_pass_c(uint32_t scratch, uint32_t result, int
   }
 }
 
-template <int BITS, bool F16OP>
-__global__ void __launch_bounds__(kPwThreads, 2)
+template <int BITS, bool F16OP, int TW = kPwWarps>
+__global__ void __launch_bounds__(pw_threads(TW), (TW == kPwWarps ? 2 : 1))
 rotate_quantize_warp_kernel(const WarpPrologueParams p) {
+  constexpr int kPwThreads = pw_threads(TW);
+
   extern __shared__ unsigned char pw_smem_raw[];
   constexpr int kLevels = 1 << BITS;
   constexpr int kMaxCells = pw_max_cells(BITS);
@@ -405,7 +411,7 @@ rotate_quantize_warp_kernel(const WarpPrologueParams p) {
   const int block = 1 << p.log2_block;
   const int R = p.batch_rows;
   const int S = p.slots;
-  const PwLayout lay = pw_layout(dim, block, R, S, BITS);
+  const PwLayout lay = pw_layout(dim, block, R, S, BITS, TW);
 
   // bytes 0..63: full[4] normed[4] barriers; 64..79: done counters; 80..: flags
   int *s_done = reinterpret_cast<int *>(smem + 64);
@@ -433,6 +439,8 @@ rotate_quantize_warp_kernel(const WarpPrologueParams p) {
   // clearing for the kernel that follows (both off every token's critical path).
   const int workers = static_cast<int>(gridDim.x) - (p.table_scale_out != nullptr ? 1 : 0);
   if (static_cast<int>(blockIdx.x) == workers) {
+    // its outputs live in the workspace, which the kernel before this one may still read
+    asm volatile("griddepcontrol.wait;" ::: "memory");
     if (threadIdx.x < 256) {
       for (int i = threadIdx.x; i < p.zero_count; i += 256) {
         p.zero_words[i] = 0;
@@ -466,9 +474,6 @@ rotate_quantize_warp_kernel(const WarpPrologueParams p) {
     *s_fallback = 0;
     *s_abort = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-    for (int b = 0; b < S && b < my_batches; ++b) {
-      issue_load(b);
-    }
   }
   for (int i = threadIdx.x; i < kLevels; i += kPwThreads) {
     s_cent[i] = p.centroids[i];
@@ -593,11 +598,21 @@ rotate_quantize_warp_kernel(const WarpPrologueParams p) {
   const PwCellMap map = pw_cell_map(lo, hi, use_cells ? cells : 8);
   const int units_per_row = block > kPwChunk ? dim / block : (dim + kPwChunk - 1) / kPwChunk;
 
-  if (warp >= kPwWarps) {
+  // Everything above read constants only (codebook, permutation, signs) and may have run while
+  // the kernel before this one in the stream was still busy.  From here on the kernel reads x and
+  // writes its outputs, which that kernel may have produced or may still be reading.
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+  if (threadIdx.x == 0) {
+    for (int b = 0; b < S && b < my_batches; ++b) {
+      issue_load(b);
+    }
+  }
+
+  if (warp >= TW) {
     // ================= norm warps: alternate batches =================
     const int r = lane >> 3;
     const int t = lane & 7;
-    for (int bi = warp - kPwWarps; bi < my_batches; bi += kPwNormWarps) {
+    for (int bi = warp - TW; bi < my_batches; bi += kPwNormWarps) {
       const int slot = bi % S;
       const uint32_t use = static_cast<uint32_t>(bi / S);
       const int64_t row0 = (static_cast<int64_t>(blockIdx.x) + static_cast<int64_t>(bi) * workers) * R;
@@ -693,7 +708,7 @@ rotate_quantize_warp_kernel(const WarpPrologueParams p) {
 
   // ================= transform warps =================
   const int team_size = block > kPwChunk ? block / kPwChunk : 1;
-  const int n_teams = kPwWarps / team_size;
+  const int n_teams = TW / team_size;
   const int team = warp / team_size;
   const int tw = warp - team * team_size;
   const int team_threads = team_size * 32;
@@ -824,7 +839,7 @@ rotate_quantize_warp_kernel(const WarpPrologueParams p) {
     __syncwarp();
     if (lane == 0) {
       __threadfence_block();
-      if (atomicAdd(&s_done[slot], 1) == kPwWarps - 1) {
+      if (atomicAdd(&s_done[slot], 1) == TW - 1) {
         atomicExch(&s_done[slot], 0);
         if (bi + S < my_batches) {
           pw_fence_async();
