@@ -745,6 +745,19 @@ gemm_w4_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
   // as this grid's last wave drains; it touches nothing of ours before its own wait.
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   asm volatile("griddepcontrol.wait;" ::: "memory");
+  // The copies of the first stages leave before the tables below are built: their latency is
+  // the longest item of the pipeline fill.
+  int issued_early = 0;
+  if (warp == T::kProducerWarp && lane == 0) {
+    for (; issued_early < T::kStages && issued_early < p.k_iters; ++issued_early) {
+      const int s = issued_early;
+      mbar_arrive_expect_tx(full_bar(s), T::kABytes + (T::kPackedByTma ? T::kPBytes : 0));
+      tma_load_2d(a_addr(s), &map_a, full_bar(s), s * kBK, static_cast<int>(m0));
+      if (T::kPackedByTma) {
+        tma_load_2d(smem_u32(p_ptr(s)), &map_p, full_bar(s), s * T::kRowBytes, static_cast<int>(n0));
+      }
+    }
+  }
   // chosen by the kernel that ran just before this one (table_scale.cuh); 2^8 without it
   const float table_scale =
       SCALED ? 1.0f : (p.table_scale != nullptr ? __ldg(p.table_scale) : kCentroidScale);
@@ -770,8 +783,8 @@ gemm_w4_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
 
   if (warp == T::kProducerWarp) {
     if (lane == 0) {
-      int issued = 0;
-      for (int it = 0; it < p.k_iters; ++it) {
+      int issued = issued_early;
+      for (int it = issued_early; it < p.k_iters; ++it) {
         const int s = it % T::kStages;
         const uint32_t phase = (it / T::kStages) & 1u;
         if (!mbar_wait(empty_bar(s), phase ^ 1u, s_abort, 1)) {
