@@ -88,3 +88,37 @@ def test_large_batches_take_the_warp_kernel_by_default(oracle):
     ref, _c, _n = oracle.quantize_activations(x[pick], rot.permutation, rot.signs, block, cb.boundaries,
                                               cb.centroids, eps=1e-10, norm_order=oracle.NORM_AVX512)
     assert torch.equal(bits_of(xq[pick]), bits_of(ref))
+
+
+def test_chained_layers_respect_stream_order():
+    """Prologue and GEMM are launched programmatically (each may start while the kernel before
+    it drains) and wait for their predecessor before touching its output.  Three dependent
+    layers enqueued back to back must give the bits of the same layers run with a device
+    synchronisation in between, every time."""
+    dev = _dev()
+    torch.manual_seed(11)
+    cfg = OrbitQuantConfig(weight_bits=4, activation_bits=4, rotation_seed=2)
+    dims = [(768, 1536), (1536, 768), (768, 1024)]
+    layers = []
+    for k, n in dims:
+        lin = torch.nn.Linear(k, n)
+        with torch.no_grad():
+            lin.weight.mul_(0.05 / lin.weight.std())
+        layers.append(OrbitQuantLinear.from_linear(lin, config=cfg, module_name=f"l{k}").to(dev))
+    x = torch.randn(2304, 768).to(torch.bfloat16).to(dev)   # >= 2048 rows: the warp-per-block prologue
+    assert "rotate_quantize" in native.forward_kernel_name(2304, 768, 1536, 4, 4, layers[0].rotation.block_size)
+
+    def run(sync):
+        h = x
+        for layer in layers:
+            h = layer(h)
+            if sync:
+                torch.cuda.synchronize()
+        return h
+
+    native.gemm_clear_device_status()
+    reference = run(sync=True)
+    for _ in range(6):
+        assert torch.equal(run(sync=False), reference)
+    torch.cuda.synchronize()
+    assert native.gemm_device_status() == 0
