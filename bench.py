@@ -727,7 +727,8 @@ def main():
     host_x = synth_activations(rows, layers[0][0].k, 7, spec["outliers"]).pin_memory()
     host_y = torch.empty((rows, layers[-1][0].n), dtype=torch.bfloat16).pin_memory()
     chain = block_chain(layers, lambda i, x, _full: layers[i][1](x))
-    e2e_ms, e2e_steps = time_e2e(chain, host_x, host_y, device, args.steps, lambda: torch.cuda.synchronize())
+    e2e_ms, e2e_steps, e2e_mode = time_e2e(chain, host_x, host_y, device, args.steps,
+                                           lambda: torch.cuda.synchronize(), use_graph=True)
     total_flops = sum(layer_flops(rows, l.k, l.n) for l, _m in layers)
 
     roofline = result["roofline"]
@@ -753,7 +754,9 @@ def main():
                 "ms_per_step": e2e_ms / e2e_steps,
                 "what": "OrbitQuantLinear modules chained as DiT block(s) (QKV, out, MLP up, GELU, "
                         "MLP down); pinned host input and output, copies on side streams "
-                        "overlapping the neighbouring steps"},
+                        "overlapping the neighbouring steps",
+                "launch": ("sixteen steps per CUDA graph replay, host copies inside the graph"
+                           if e2e_mode == "graph" else "eager, one C call per layer")},
         "gpu_launches": result["gpu_launches"], "clocks": clocks,
         "us_per_layer": result["us_per_layer"],
     }
@@ -798,10 +801,13 @@ def main():
     print(json.dumps(line))
 
 
-def time_e2e(chain, host_x, host_y, device, steps, barrier):
+def time_e2e(chain, host_x, host_y, device, steps, barrier, use_graph=False):
     """Every step copies its input from pinned host memory and its result back; the copies of
     neighbouring steps run on two side streams so that PCIe transfers overlap the kernels
-    (double-buffered device input, as a serving loop would do)."""
+    (double-buffered device input, as a serving loop would do).  With `use_graph` sixteen such steps
+    are also captured in one CUDA graph (copies included) and replayed, which takes the host's
+    launch overhead out of the measurement; the faster of the two ways is returned.
+    Returns (milliseconds, steps, "graph" | "eager")."""
     copy_in, copy_out = torch.cuda.Stream(), torch.cuda.Stream()
     dev_x = [torch.empty_like(host_x, device=device) for _ in range(2)]
     x_ready = [torch.cuda.Event() for _ in range(2)]
@@ -830,6 +836,48 @@ def time_e2e(chain, host_x, host_y, device, steps, barrier):
         e2e_step(i)
     main_stream.wait_stream(copy_out)
     barrier()
+
+    graph = None
+    steps_per_replay = 16   # a replay starts and ends with an exposed copy: amortise them
+    if use_graph:
+        try:
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph):
+                cap = torch.cuda.current_stream()
+                fork = torch.cuda.Event()
+                fork.record(cap)
+                copy_in.wait_event(fork)       # the side streams join the capture
+                copy_out.wait_event(fork)
+                free = [None, None]
+                for i in range(steps_per_replay):
+                    b = i & 1
+                    with torch.cuda.stream(copy_in):
+                        if free[b] is not None:
+                            copy_in.wait_event(free[b])
+                        dev_x[b].copy_(host_x, non_blocking=True)
+                        ready = torch.cuda.Event()
+                        ready.record(copy_in)
+                    cap.wait_event(ready)
+                    h = chain(dev_x[b])
+                    free[b] = torch.cuda.Event()
+                    free[b].record(cap)
+                    with torch.cuda.stream(copy_out):
+                        copy_out.wait_event(free[b])
+                        host_y.copy_(h, non_blocking=True)
+                cap.wait_stream(copy_in)
+                cap.wait_stream(copy_out)
+            for _ in range(2):
+                graph.replay()
+            torch.cuda.synchronize()
+        except Exception as exc:  # eager timing below
+            print(f"[bench] end-to-end graph capture failed ({type(exc).__name__}: {exc}); timing eagerly",
+                  file=sys.stderr)
+            graph = None
+            torch.cuda.synchronize()
+
+    # Both ways of driving the same calls are timed and the faster one is reported: the eager loop
+    # overlaps the copies of ALL neighbouring steps but depends on the host keeping up with one C
+    # call per layer; the graph needs no host work but exposes one copy at each end of a replay.
     e_start, e_stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e2e_steps = max(4, steps // 2 * 2)
     e_start.record()
@@ -839,7 +887,19 @@ def time_e2e(chain, host_x, host_y, device, steps, barrier):
     main_stream.wait_stream(copy_in)
     e_stop.record()
     barrier()
-    return e_start.elapsed_time(e_stop), e2e_steps
+    best = (e_start.elapsed_time(e_stop), e2e_steps, "eager")
+    if graph is not None:
+        replays = max(1, (steps + steps_per_replay - 1) // steps_per_replay)
+        g_start, g_stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        g_start.record()
+        for _ in range(replays):
+            graph.replay()
+        g_stop.record()
+        barrier()
+        graph_ms = g_start.elapsed_time(g_stop)
+        if graph_ms / (replays * steps_per_replay) < best[0] / best[1]:
+            best = (graph_ms, replays * steps_per_replay, "graph")
+    return best
 
 
 def run_multi_gpu(args, device, rank, world, local_rank):
@@ -966,7 +1026,7 @@ def run_multi_gpu(args, device, rank, world, local_rank):
         return gather_columns(share, k_next)
 
     chain = block_chain(layers, e2e_forward)
-    e2e_ms, e2e_steps = time_e2e(chain, host_x, host_y, device, args.steps, barrier)
+    e2e_ms, e2e_steps, _e2e_mode = time_e2e(chain, host_x, host_y, device, args.steps, barrier)
     t = torch.tensor([e2e_ms], device=device)
     dist.all_reduce(t, op=dist.ReduceOp.MAX)
     e2e_ms = float(t.item())
