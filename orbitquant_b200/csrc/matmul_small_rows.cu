@@ -79,6 +79,31 @@ __global__ void __launch_bounds__(kMaxWarps * 32) small_rows_w4_kernel(const Sma
   const int t = lane & 3;
   const int64_t n0 = static_cast<int64_t>(blockIdx.x) * 8 * p.nb;
 
+  // This CTA's weight rows on their way into the L2 (they do not depend on the kernel before
+  // this one, whose tail this kernel's start overlaps): with the weights cold in HBM their
+  // latency would otherwise sit between the dependency wait and the first MMA.
+  {
+    const int64_t prefetch_row_bytes = p.in_features / 2;
+    const int64_t n_end = min(p.out_features, n0 + 8 * static_cast<int64_t>(p.nb));
+    const unsigned char *first = reinterpret_cast<const unsigned char *>(p.packed) + n0 * prefetch_row_bytes;
+    const int64_t bytes = n_end > n0 ? (n_end - n0) * prefetch_row_bytes : 0;
+    for (int64_t off = static_cast<int64_t>(threadIdx.x) * 128; off < bytes;
+         off += static_cast<int64_t>(blockDim.x) * 128) {
+      asm volatile("prefetch.global.L2 [%0];" ::"l"(first + off));
+    }
+    // the epilogue's per-column operands likewise (one line each covers this CTA's columns)
+    if (threadIdx.x == 0 && n0 < p.out_features) {
+      asm volatile("prefetch.global.L2 [%0];" ::"l"(p.row_norms + n0));
+      if (p.bias_dtype >= 0) {
+        asm volatile("prefetch.global.L2 [%0];" ::"l"(static_cast<const unsigned char *>(p.bias) +
+                                                       n0 * (p.bias_dtype == OQ_DTYPE_F32 ? 4 : 2)));
+      }
+    }
+  }
+
+  // the next kernel in the stream (the next layer's prologue) may start its own prefetches
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+
   if (SCALED) {
     if (threadIdx.x < 16) {
       s_cent[threadIdx.x] = p.centroids[threadIdx.x];

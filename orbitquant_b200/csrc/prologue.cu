@@ -720,8 +720,24 @@ int launch_rotate_quantize(const void *x, int x_dtype, int64_t rows, int64_t dim
     OQ_CHECK_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                        static_cast<int>(smem)));
   }
-  kernel<<<grid, kThreads, smem, stream>>>(p);
-  OQ_CHECK_CUDA(cudaGetLastError());
+  if (fast != nullptr) {
+    // programmatic stream serialization: the kernel prefetches its constants and then waits
+    // for the kernel before it (griddepcontrol.wait at its top)
+    cudaLaunchConfig_t config = {};
+    config.gridDim = dim3(static_cast<unsigned>(grid));
+    config.blockDim = dim3(kThreads);
+    config.dynamicSmemBytes = smem;
+    config.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    config.attrs = attr;
+    config.numAttrs = 1;
+    OQ_CHECK_CUDA(cudaLaunchKernelEx(&config, kernel, p));
+  } else {
+    kernel<<<grid, kThreads, smem, stream>>>(p);
+    OQ_CHECK_CUDA(cudaGetLastError());
+  }
   count_launch();
   return OQ_OK;
 }

@@ -306,6 +306,25 @@ rotate_quantize_fast_kernel(const PrologueParams p) {
   uint16_t *s_outtab = reinterpret_cast<uint16_t *>(s_opscale + 8);                 // [R][kLevels]
 
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");  // see rotate_quantize_kernel
+  // Launched with programmatic stream serialization: while the kernel before this one drains,
+  // the constants of THIS layer (its own permutation, signs and codebook: cold in a chain of
+  // layers) are already on their way into the L2.  x, the outputs and the workspace are touched
+  // after the wait only.
+  {
+    const unsigned char *perm_bytes = reinterpret_cast<const unsigned char *>(p.perm);
+    const unsigned char *sign_bytes = reinterpret_cast<const unsigned char *>(p.signs);
+    for (int off = threadIdx.x * 128; off < dim * 4; off += kFastThreads * 128) {
+      asm volatile("prefetch.global.L2 [%0];" ::"l"(perm_bytes + off));
+    }
+    for (int off = threadIdx.x * 128; off < dim; off += kFastThreads * 128) {
+      asm volatile("prefetch.global.L2 [%0];" ::"l"(sign_bytes + off));
+    }
+    if (threadIdx.x == 0) {
+      asm volatile("prefetch.global.L2 [%0];" ::"l"(p.centroids));
+      asm volatile("prefetch.global.L2 [%0];" ::"l"(p.boundaries));
+    }
+  }
+  asm volatile("griddepcontrol.wait;" ::: "memory");
   // The last CTA of the grid does nothing but the table-scale search and the counter clearing,
   // so that with few rows (decode) they are not on any token's critical path.
   const int workers = static_cast<int>(gridDim.x) - (p.table_scale_out != nullptr ? 1 : 0);
