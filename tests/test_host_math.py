@@ -303,3 +303,24 @@ def test_argument_errors_surface_without_a_gpu():
         native.matmul_packed_weight(torch.zeros(2, 64), torch.zeros(256, dtype=torch.uint8),
                                     torch.zeros(8), torch.zeros(16), bits=4, out_features=8,
                                     in_features=64)
+
+
+def test_kernel_plan_by_shape_without_a_gpu():
+    """`oq_linear_kernel_name` answers from the shape alone (no launch, no device): the dispatch
+    rules of the forward -- one launch for a few tokens of a small layer, the few-token tensor-core
+    kernel up to 128 rows, the CTA-pair kernel where a 512-row pair tile fills the machine, the
+    single-CTA kernel for 6- and 8-bit weights and for small grids, the general kernel otherwise."""
+    from orbitquant_b200 import native
+
+    plan = native.forward_kernel_name
+    assert plan(1, 768, 2304, 4, 6, 256) == "decode_fused_kernel"
+    assert plan(16, 768, 2304, 4, 6, 256) == "rotate_quantize + small_rows_w4_kernel"
+    assert plan(16, 3072, 9216, 4, 4, 1024) == "rotate_quantize + skinny_tcgen05_kernel"
+    assert plan(128, 3072, 3072, 4, 4, 1024) == "rotate_quantize + skinny_tcgen05_kernel"
+    assert plan(300, 768, 512, 4, 4, 256) == "rotate_quantize + gemm_w4_tcgen05_kernel"
+    assert plan(4608, 3072, 9216, 4, 4, 1024) == "rotate_quantize + gemm_pair_tcgen05_kernel"
+    assert plan(32760, 5120, 15360, 4, 4, 1024) == "rotate_quantize + gemm_pair_tcgen05_kernel"
+    assert plan(4096, 3072, 3072, 3, 3, 1024) == "rotate_quantize + gemm_pair_tcgen05_kernel"
+    assert plan(4608, 3072, 3072, 6, 6, 1024) == "rotate_quantize + gemm_w4_tcgen05_kernel"
+    assert plan(40, 200, 96, 3, 3, 8) == "rotate_quantize + tiled_matmul_kernel"
+    assert plan(0, 768, 768, 4, 4, 256) == "none"
