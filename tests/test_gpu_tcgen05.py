@@ -262,3 +262,31 @@ def test_tcgen05_table_without_sign_symmetry(oracle, pair, tunables):
     ref = oracle.matmul_packed(x, packed, rn, cent, bits=4, out_features=n, bias=bias,
                                mode=oracle.MM_FP32_CENTROIDS)
     _check_close(y, ref, ("asymmetric table", pair))
+
+
+def test_tcgen05_cta_pair_hand_over_under_load(tunables):
+    """Several waves of pair tiles, launched back to back many times: every k step of every tile
+    hands the peer CTA's half of the weight tile to the leader's MMAs; a hand-over that let the
+    MMAs read a half-written tile would show as a difference from the single-CTA kernel's bits."""
+    dev = _dev()
+    rows, k, n = 2560, 1024, 4608
+    g = torch.Generator().manual_seed(5)
+    packed = torch.randint(0, 256, (k * n // 2,), generator=g, dtype=torch.uint8).to(dev)
+    rn = (torch.rand(n, generator=g) + 0.5).to(torch.bfloat16).to(dev)
+    cent = get_codebook(k, 4).centroids.to(dev)
+    x = torch.randn(rows, k, generator=g).to(torch.bfloat16).to(dev)
+    op, scale, table = native.rows_to_f16_operand(x, cent)
+    native.gemm_clear_device_status()
+    tunables.set("pair", 0)
+    ref = torch.empty(rows, n, dtype=torch.bfloat16, device=dev)
+    native.gemm_tcgen05_f16(op, scale, packed, rn, cent, out_features=n, out=ref, table_scale=table)
+    for width in (256, 192):
+        tunables.set("pair", width)
+        outs = [torch.empty_like(ref) for _ in range(8)]
+        for rep in range(40):
+            native.gemm_tcgen05_f16(op, scale, packed, rn, cent, out_features=n, out=outs[rep % 8],
+                                    table_scale=table)
+            if rep % 8 == 7:
+                torch.cuda.synchronize()
+                assert all(torch.equal(o, ref) for o in outs), (width, rep)
+    _assert_status_clean()
