@@ -14,7 +14,7 @@ std::atomic<uint64_t> g_launch_count{0};
 namespace {
 const char *const kTunableNames[OQ_TUNE_COUNT] = {
     "TILE_N", "TILE_ORDER", "SKINNY", "STREAM_ROWS", "PROLOGUE_ROWS", "SKINNY_UNITS_PER_SM",
-    "SKINNY_MIN_ITERS", "FUSED_DECODE", "PROLOGUE_KERNEL", "PAIR"};
+    "SKINNY_MIN_ITERS", "FUSED_DECODE", "PROLOGUE_KERNEL", "PAIR", "INT8_MMA"};
 std::atomic<int> g_tunables[OQ_TUNE_COUNT];
 std::once_flag g_tunables_once;
 
@@ -50,6 +50,15 @@ int launch_rotate_quantize(const void *x, int x_dtype, int64_t rows, int64_t dim
                            const float *w_centroids, int w_bits, float *table_scale_out,
                            int *zero_words, int zero_count, cudaStream_t stream,
                            const float *given_norms = nullptr, const int8_t *code_map = nullptr);
+bool tcgen05_i8_supported(int64_t rows, int64_t in_features, int64_t out_features, int bits);
+int launch_tcgen05_gemm_i8(void *out, const void *a_int8, const float *row_scale, const float *table_scale,
+                           int64_t rows, int64_t in_features, int64_t out_features, const uint8_t *packed,
+                           const void *row_norms_bf16, const float *code_floats, const void *bias,
+                           int bias_dtype, cudaStream_t stream);
+int launch_expand_packed_a4_int8(const uint8_t *packed_act, const float *token_norms, const int8_t *act_codes,
+                                 const int8_t *w_codes, int w_levels, float scale, int64_t rows, int64_t dim,
+                                 void *out_int8, float *row_scale, float *table_scale, float *w_code_floats,
+                                 cudaStream_t stream);
 int launch_expand_packed_a4(const uint8_t *packed_act, const float *token_norms, const int8_t *act_codes,
                             const int8_t *w_codes, int w_levels, float scale, int64_t rows, int64_t dim,
                             void *out_f16, float *row_scale, float *table_scale, float *w_code_floats,
@@ -433,6 +442,17 @@ int oq_matmul_packed_w4a4_int8(void *out, const uint8_t *packed_act, const uint8
   float *row_scale = reinterpret_cast<float *>(ws + f16_operand_bytes(rows, in_features));
   float *table_scale = row_scale + rows;
   float *code_floats = reinterpret_cast<float *>(ws + tcgen05_head_bytes(rows, in_features));
+  // Large batches of a W4 layer: INT8 operands on the tensor cores (kind::i8), the integer
+  // contraction the reference's kernels perform (packed_matmul.cu:744-1009), exact in int32.
+  if (tcgen05_i8_supported(rows, in_features, out_features, weight_bits) && tunable(OQ_TUNE_INT8_MMA) != 0) {
+    if (int rc = launch_expand_packed_a4_int8(packed_act, token_norms, act_codes, weight_codes,
+                                              1 << weight_bits, act_scale * weight_scale, rows, in_features,
+                                              workspace, row_scale, table_scale, code_floats, s)) {
+      return rc;
+    }
+    return launch_tcgen05_gemm_i8(out, workspace, row_scale, table_scale, rows, in_features, out_features,
+                                  packed_weight, row_norms_bf16, code_floats, bias, bias_dtype, s);
+  }
   if (int rc = launch_expand_packed_a4(packed_act, token_norms, act_codes, weight_codes, 1 << weight_bits,
                                        act_scale * weight_scale, rows, in_features, workspace, row_scale,
                                        table_scale, code_floats, s)) {

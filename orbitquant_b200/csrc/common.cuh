@@ -37,6 +37,7 @@ enum {
   OQ_TUNE_FUSED_DECODE,          // 0 = rows <= 16 never take the single-launch fused kernel
   OQ_TUNE_PROLOGUE_KERNEL,       // 0 = general, 1 = multi-token CTA, 2 = warp-per-block kernel
   OQ_TUNE_PAIR,                  // large-row tcgen05 kernel: 0 / 1 = never / always the CTA-pair variant
+  OQ_TUNE_INT8_MMA,              // INT8-surrogate matmul: 0 = INT8 codes as f16 on the f16 kernel, never kind::i8
   OQ_TUNE_COUNT
 };
 int tunable(int which);

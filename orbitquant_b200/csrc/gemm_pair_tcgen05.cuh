@@ -31,13 +31,18 @@
 // init, before tensor-memory release) are hardware barriers that every thread of both CTAs
 // reaches on every path.
 
-template <int BN, int BITS>
+// I8: INT8 operands (kind::i8, 32-bit integer accumulators) -- a k step is 128 values, i.e. the
+// same 128-byte operand rows as 64 values of a 16-bit type.
+template <int BN, int BITS, bool I8 = false>
 struct PairTile {
   static constexpr int kBN = BN;           // pair tile width (256 or 192)
   static constexpr int kHalfN = BN / 2;    // weight rows expanded by one CTA
+  static constexpr bool kI8 = I8;
+  static constexpr int kStepElems = I8 ? 2 * kBK : kBK;   // k values per pipeline step
   static constexpr int kABytes = kBM * kBK * 2;
   static constexpr int kBBytes = kHalfN * kBK * 2;
-  static constexpr int kRowBytes = kBK * BITS / 8;
+  static constexpr int kRowBytes = kStepElems * BITS / 8;
+  static_assert(!I8 || BITS == 4, "INT8 code tables exist for 4-bit indices");
   static constexpr bool kPackedByTma = BITS != 3;
   static constexpr int kPBytes = kPackedByTma ? kHalfN * kRowBytes : 0;
   static constexpr int kStageBytes = (kABytes + kBBytes + kPBytes + 1023) / 1024 * 1024;
@@ -107,6 +112,16 @@ __device__ __forceinline__ void umma_f16_pair(uint32_t tmem_d, uint64_t desc_a, 
       : "memory");
 }
 
+__device__ __forceinline__ void umma_i8_pair(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b,
+                                             uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::2.kind::i8 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+
 // Arrives on the barrier at this shared-memory offset in every CTA of `mask`.
 __device__ __forceinline__ void umma_commit_pair(uint32_t bar, uint16_t mask) {
   asm volatile(
@@ -115,17 +130,24 @@ __device__ __forceinline__ void umma_commit_pair(uint32_t bar, uint16_t mask) {
       : "memory");
 }
 
+// Instruction descriptor of the INT8 pair MMA: 32-bit integer accumulator (format code 2),
+// A = B = signed 8-bit (format code 1), K-major, M = 256, 32 k values per instruction.
+__host__ __device__ constexpr uint32_t instr_desc_pair_i8(int n) {
+  return (2u << 4) | (1u << 7) | (1u << 10) | (static_cast<uint32_t>(n >> 3) << 17) |
+         (static_cast<uint32_t>(256 >> 4) << 24);
+}
+
 // Instruction descriptor of the pair MMA: as instr_desc(), M = 256.
 __host__ __device__ constexpr uint32_t instr_desc_pair(int n, bool bf16_operands) {
   return (1u << 4) | ((bf16_operands ? 1u : 0u) << 7) | ((bf16_operands ? 1u : 0u) << 10) |
          (static_cast<uint32_t>(n >> 3) << 17) | (static_cast<uint32_t>(256 >> 4) << 24);
 }
 
-template <int BN, int BITS, bool SCALED>
-__global__ void __launch_bounds__((PairTile<BN, BITS>::kThreads), 1)
+template <int BN, int BITS, bool SCALED, bool I8 = false>
+__global__ void __launch_bounds__((PairTile<BN, BITS, I8>::kThreads), 1)
 gemm_pair_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
                          const __grid_constant__ CUtensorMap map_p, const GemmParams p) {
-  using T = PairTile<BN, BITS>;
+  using T = PairTile<BN, BITS, I8>;
   extern __shared__ __align__(16) unsigned char smem_raw[];
   // header: barriers | scale[BN] | bias[BN] | codebook
   uint64_t *bars = reinterpret_cast<uint64_t *>(smem_raw);
@@ -194,7 +216,7 @@ gemm_pair_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
     for (; issued_early < T::kStages && issued_early < p.k_iters; ++issued_early) {
       const int s = issued_early;
       mbar_arrive_expect_tx(full_bar(s), T::kABytes + T::kPBytes);
-      tma_load_2d(a_addr(s), &map_a, full_bar(s), s * kBK, static_cast<int>(m0));
+      tma_load_2d(a_addr(s), &map_a, full_bar(s), s * T::kStepElems, static_cast<int>(m0));
       if (T::kPackedByTma) {
         tma_load_2d(p_addr(s), &map_p, full_bar(s), s * T::kRowBytes, static_cast<int>(nb0));
       }
@@ -221,7 +243,7 @@ gemm_pair_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
           break;
         }
         mbar_arrive_expect_tx(full_bar(s), T::kABytes + T::kPBytes);
-        tma_load_2d(a_addr(s), &map_a, full_bar(s), it * kBK, static_cast<int>(m0));
+        tma_load_2d(a_addr(s), &map_a, full_bar(s), it * T::kStepElems, static_cast<int>(m0));
         if (T::kPackedByTma) {
           tma_load_2d(p_addr(s), &map_p, full_bar(s), it * T::kRowBytes, static_cast<int>(nb0));
         }
@@ -240,7 +262,7 @@ gemm_pair_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
     }
   } else if (warp == T::kMmaWarp) {
     if (lane == 0 && rank == 0) {
-      constexpr uint32_t idesc = instr_desc_pair(BN, SCALED);
+      constexpr uint32_t idesc = I8 ? instr_desc_pair_i8(BN) : instr_desc_pair(BN, SCALED);
       bool ok = true;
       for (int it = 0; it < p.k_iters && ok; ++it) {
         const int s = it % T::kStages;
@@ -257,7 +279,12 @@ gemm_pair_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
           for (int j = 0; j < kBK / 16; ++j) {
             const uint64_t da = smem_desc_k_sw128(a_addr(s) + half * (128 * 128) + j * 32);
             const uint64_t db = smem_desc_k_sw128(b_addr(s) + j * 32);
-            umma_f16_pair(tmem_base + half * BN, da, db, idesc, (it > 0 || j > 0) ? 1u : 0u);
+            // four instructions of 32 operand bytes each: 16 k values of a 16-bit type, 32 of INT8
+            if (I8) {
+              umma_i8_pair(tmem_base + half * BN, da, db, idesc, (it > 0 || j > 0) ? 1u : 0u);
+            } else {
+              umma_f16_pair(tmem_base + half * BN, da, db, idesc, (it > 0 || j > 0) ? 1u : 0u);
+            }
           }
         }
         umma_commit_pair(empty_bar(s), 3);
@@ -296,14 +323,14 @@ gemm_pair_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
   }
 }
 
-template <int BN, int BITS, bool SCALED>
+template <int BN, int BITS, bool SCALED, bool I8 = false>
 int launch_pair_bn(const CUtensorMap &map_a, const CUtensorMap &map_p, const GemmParams &p,
                    int pairs, cudaStream_t stream) {
-  using T = PairTile<BN, BITS>;
+  using T = PairTile<BN, BITS, I8>;
   static std::once_flag once;
   static cudaError_t attr_status = cudaSuccess;
   std::call_once(once, [] {
-    attr_status = cudaFuncSetAttribute(gemm_pair_tcgen05_kernel<BN, BITS, SCALED>,
+    attr_status = cudaFuncSetAttribute(gemm_pair_tcgen05_kernel<BN, BITS, SCALED, I8>,
                                        cudaFuncAttributeMaxDynamicSharedMemorySize, T::kSmemBytes);
   });
   OQ_CHECK_CUDA(attr_status);
@@ -321,7 +348,7 @@ int launch_pair_bn(const CUtensorMap &map_a, const CUtensorMap &map_p, const Gem
   attr[1].val.programmaticStreamSerializationAllowed = 1;
   config.attrs = attr;
   config.numAttrs = 2;
-  OQ_CHECK_CUDA(cudaLaunchKernelEx(&config, gemm_pair_tcgen05_kernel<BN, BITS, SCALED>, map_a, map_p, p));
+  OQ_CHECK_CUDA(cudaLaunchKernelEx(&config, gemm_pair_tcgen05_kernel<BN, BITS, SCALED, I8>, map_a, map_p, p));
   count_launch();
   return OQ_OK;
 }

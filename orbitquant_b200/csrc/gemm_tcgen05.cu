@@ -64,6 +64,8 @@ constexpr double kPairRate192 = 0.98;
 template <int BN, int BITS>
 struct Tile {
 
+  static constexpr bool kI8 = false;                   // 16-bit operands
+  static constexpr int kStepElems = kBK;               // k values per pipeline step
   static constexpr int kABytes = kBM * kBK * 2;        // 32 KB
   static constexpr int kBBytes = BN * kBK * 2;         // expanded f16 tile
   static constexpr int kRowBytes = kBK * BITS / 8;     // packed bytes of one weight row per k step
@@ -345,6 +347,24 @@ __device__ __forceinline__ bool table_is_symmetric(const RegTable &t) {
          t.hi[1] == (__byte_perm(t.hi[2], 0u, 0x0123u) ^ 0x80808080u);
 }
 
+// INT8 code table (4-bit indices -> one signed byte each): sixteen entries in four registers,
+// eight indices -> eight bytes.
+__device__ __forceinline__ void decode8_w4_bytes(uint32_t w, const uint32_t (&tb)[4], uint32_t &r0, uint32_t &r1) {
+  const uint32_t low3 = w & 0x77777777u;
+  const uint32_t bit3 = (w >> 3) & 0x11111111u;
+  uint32_t r[2];
+#pragma unroll
+  for (int h = 0; h < 2; ++h) {
+    const uint32_t sel = low3 >> (16 * h);
+    const uint32_t mask = __byte_perm(0x0000ff00u, 0u, bit3 >> (16 * h));
+    const uint32_t x = __byte_perm(tb[0], tb[1], sel);
+    const uint32_t y = __byte_perm(tb[2], tb[3], sel);
+    r[h] = (x & ~mask) | (y & mask);
+  }
+  r0 = r[0];
+  r1 = r[1];
+}
+
 // 3-bit: 24 bits; spread each 3-bit field to its own selector nibble.
 __device__ __forceinline__ void decode8_w3(uint32_t w, const RegTable &t, uint4 &out) {
   uint32_t r[4];
@@ -418,7 +438,7 @@ __device__ __forceinline__ bool expand_weight_tiles(const GemmParams &p, int64_t
   constexpr int kThreadsPerRow = T::kTpr;
   constexpr int kBytesPerThread = T::kRowBytes / kThreadsPerRow;
   constexpr int kWords = kBytesPerThread / 4;
-  constexpr int kGroups = (kBK / 8) / kThreadsPerRow;   // 16-byte output chunks per thread
+  constexpr int kGroups = 8 / kThreadsPerRow;   // 16-byte chunks of the 128-byte output row per thread
   const int et = threadIdx.x;  // expander thread index (every expander warp owns rows)
   const int row = et / kThreadsPerRow;
   const int part = et % kThreadsPerRow;
@@ -445,9 +465,21 @@ __device__ __forceinline__ bool expand_weight_tiles(const GemmParams &p, int64_t
     table.hi[q] = hi;
     table.lo[q] = lo;
   }
+  // INT8 operands: the codebook holds the (integer-valued) code table
+  uint32_t byte_table[4] = {0u, 0u, 0u, 0u};
+  if (T::kI8) {
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const int code = __float2int_rn(s_cent[4 * q + e]);
+        byte_table[q] |= (static_cast<uint32_t>(code) & 0xffu) << (8 * e);
+      }
+    }
+  }
   const uint16_t *lane_lut = s_lut + (BITS == 6 ? lane : (lane & 7));
   // the symmetric decode is taken by the whole warp or not at all
-  const bool symmetric = BITS == 4 && __all_sync(0xffffffffu, table_is_symmetric(table));
+  const bool symmetric = BITS == 4 && !T::kI8 && __all_sync(0xffffffffu, table_is_symmetric(table));
   const uint32_t row_off = (row >> 3) * 1024 + (row & 7) * 128;
   // Shared-memory addresses of this thread's packed bytes and of the 16-byte chunks it writes,
   // in stage 0.  The k loop below is unrolled over the stages, so a stage's offset is an
@@ -554,7 +586,14 @@ __device__ __forceinline__ bool expand_weight_tiles(const GemmParams &p, int64_t
       // the (latency-bound) byte-permute sequences one after the other instead of overlapping
       // them.
       uint4 expanded[kGroups];
-      if (symmetric) {
+      if (T::kI8) {
+        // sixteen 4-bit indices (two words) per 16-byte chunk
+#pragma unroll
+        for (int c = 0; c < kGroups; ++c) {
+          decode8_w4_bytes(words[(2 * c) % kWords], byte_table, expanded[c].x, expanded[c].y);
+          decode8_w4_bytes(words[(2 * c + 1) % kWords], byte_table, expanded[c].z, expanded[c].w);
+        }
+      } else if (symmetric) {
 #pragma unroll
         for (int c = 0; c < kGroups; ++c) {
           uint32_t lo;
@@ -641,10 +680,12 @@ __device__ __forceinline__ void store_output_tile(const GemmParams &p, int64_t m
 #pragma unroll
         for (int e = 0; e < 4; ++e) {
           const int j = 4 * q + e;
-          const float a = fmaf(__uint_as_float(v[2 * j]), row_scale * s_scale[c0 + 2 * j],
-                               s_bias[c0 + 2 * j]);
-          const float b = fmaf(__uint_as_float(v[2 * j + 1]), row_scale * s_scale[c0 + 2 * j + 1],
-                               s_bias[c0 + 2 * j + 1]);
+          // the accumulator holds fp32 sums, or, with INT8 operands, 32-bit integers
+          const float acc_a = T::kI8 ? __int2float_rn(static_cast<int>(v[2 * j])) : __uint_as_float(v[2 * j]);
+          const float acc_b =
+              T::kI8 ? __int2float_rn(static_cast<int>(v[2 * j + 1])) : __uint_as_float(v[2 * j + 1]);
+          const float a = fmaf(acc_a, row_scale * s_scale[c0 + 2 * j], s_bias[c0 + 2 * j]);
+          const float b = fmaf(acc_b, row_scale * s_scale[c0 + 2 * j + 1], s_bias[c0 + 2 * j + 1]);
           const __nv_bfloat162 h = __floats2bfloat162_rn(a, b);
           w[e] = *reinterpret_cast<const uint32_t *>(&h);
         }
@@ -1020,7 +1061,8 @@ int launch_bits(int bn, const CUtensorMap &map_a, const CUtensorMap &map_p, cons
 // Output tile of the large-row kernel for a problem: `*tile_n` = width of the single-CTA tile
 // (256 | 192 | 128), `*pair_n` = width of the CTA-pair tile (256 | 192) or 0 when the single-CTA
 // kernel runs.
-void choose_tile(int64_t rows, int64_t out_features, int bits, int sm_count, int *tile_n, int *pair_n) {
+void choose_tile(int64_t rows, int64_t out_features, int bits, int sm_count, int *tile_n, int *pair_n,
+                 bool pair_only = false) {
   // Tile width.  Wider tiles move fewer shared-memory bytes per flop (the activation tile
   // is re-read once per MMA), narrower ones can fill the last wave better; pick the width
   // with the best product of the two.  The per-width rates are measured ratios.
@@ -1070,7 +1112,7 @@ void choose_tile(int64_t rows, int64_t out_features, int bits, int sm_count, int
     const double p256 = pair_score(256, kPairRate256);
     const double p192 = pair_score(192, kPairRate192);
     const int best_pair = p192 > p256 ? 192 : 256;
-    if (std::max(p256, p192) > single_score) {
+    if (std::max(p256, p192) > single_score || pair_only) {
       pair_bn = best_pair;
     }
     const int forced = tunable(OQ_TUNE_PAIR);
@@ -1079,6 +1121,9 @@ void choose_tile(int64_t rows, int64_t out_features, int bits, int sm_count, int
     } else if (forced == 192 || forced == 256) {
       pair_bn = forced;
     } else if (forced > 0) {
+      pair_bn = best_pair;
+    }
+    if (pair_only && pair_bn == 0) {
       pair_bn = best_pair;
     }
   }
@@ -1236,6 +1281,87 @@ int launch_tcgen05_gemm_scatter(void *const *outs, int n_outs, int64_t out_ld, i
     case 6: return launch_bits<6>(bn, map_a, map_p, p, grid, stream);
     default: return launch_bits<8>(bn, map_a, map_p, p, grid, stream);
   }
+}
+
+// The INT8 formulation on the tensor cores (kind::i8, 32-bit integer accumulation, CTA-pair
+// kernel): `a_int8` is the [rows, in_features] INT8 activation operand, `code_floats` the
+// (integer-valued) weight code table where the other kernels take their centroids.
+bool tcgen05_i8_supported(int64_t rows, int64_t in_features, int64_t out_features, int bits) {
+  return bits == 4 && rows > kSkMaxTokens && in_features % 128 == 0 && out_features > 0 &&
+         in_features <= (1 << 30) && rows < (1ll << 31) && out_features < (1ll << 31);
+}
+
+int launch_tcgen05_gemm_i8(void *out, const void *a_int8, const float *row_scale, const float *table_scale,
+                           int64_t rows, int64_t in_features, int64_t out_features, const uint8_t *packed,
+                           const void *row_norms_bf16, const float *code_floats, const void *bias,
+                           int bias_dtype, cudaStream_t stream) {
+  OQ_CHECK_ARG(tcgen05_i8_supported(rows, in_features, out_features, 4),
+               "the INT8 tensor-core kernel needs more than 128 rows and in_features %% 128 == 0");
+  OQ_CHECK_ARG(out != nullptr && aligned16(out) && aligned16(a_int8) && aligned16(packed),
+               "buffers must be 16-byte aligned for the tcgen05 kernel");
+  EncodeTiledFn encode = encode_tiled_fn();
+  if (encode == nullptr) {
+    return fail(OQ_ERR_CUDA, "cuTensorMapEncodeTiled is not available from this driver");
+  }
+  int device = 0;
+  int sm_count = 0;
+  OQ_CHECK_CUDA(cudaGetDevice(&device));
+  OQ_CHECK_CUDA(cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, device));
+  int bn = 0;
+  int pair_bn = 0;
+  choose_tile(rows, out_features, 4, sm_count, &bn, &pair_bn, /*pair_only=*/true);
+  const int64_t m_pairs = (rows + 2 * kBM - 1) / (2 * kBM);
+  const int64_t pair_n_tiles = (out_features + pair_bn - 1) / pair_bn;
+  OQ_CHECK_ARG(m_pairs * pair_n_tiles < (1ll << 30), "too many output tiles");
+  constexpr int kStepBytes = 128;   // INT8 values per k step = operand row bytes
+  CUtensorMap map_a;
+  CUtensorMap map_p;
+  {
+    const cuuint64_t dims[2] = {static_cast<cuuint64_t>(in_features), static_cast<cuuint64_t>(rows)};
+    const cuuint64_t strides[1] = {static_cast<cuuint64_t>(in_features)};
+    const cuuint32_t box[2] = {kStepBytes, kBM};
+    const cuuint32_t elem[2] = {1, 1};
+    const CUresult rc = encode(&map_a, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void *>(a_int8), dims,
+                               strides, box, elem, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                               CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (rc != CUDA_SUCCESS) {
+      return fail(OQ_ERR_CUDA, "cuTensorMapEncodeTiled(INT8 activations) failed with code %d", (int)rc);
+    }
+  }
+  {
+    const int64_t row_bytes = in_features / 2;
+    const cuuint64_t dims[2] = {static_cast<cuuint64_t>(row_bytes), static_cast<cuuint64_t>(out_features)};
+    const cuuint64_t strides[1] = {static_cast<cuuint64_t>(row_bytes)};
+    const cuuint32_t box[2] = {kStepBytes / 2, static_cast<cuuint32_t>(pair_bn / 2)};
+    const cuuint32_t elem[2] = {1, 1};
+    const CUresult rc = encode(&map_p, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<uint8_t *>(packed), dims,
+                               strides, box, elem, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE,
+                               CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (rc != CUDA_SUCCESS) {
+      return fail(OQ_ERR_CUDA, "cuTensorMapEncodeTiled(packed weights) failed with code %d", (int)rc);
+    }
+  }
+  GemmParams p{};
+  p.outs[0] = out;
+  p.n_outs = 1;
+  p.out_ld = out_features;
+  p.out_col = 0;
+  p.packed = packed;
+  p.row_scale = row_scale;
+  p.table_scale = table_scale;
+  p.row_norms = static_cast<const __nv_bfloat16 *>(row_norms_bf16);
+  p.centroids = code_floats;
+  p.bias = bias;
+  p.bias_dtype = bias == nullptr ? -1 : bias_dtype;
+  p.rows = rows;
+  p.out_features = out_features;
+  p.k_iters = static_cast<int>(in_features / kStepBytes);
+  p.m_tiles = static_cast<int>(m_pairs);
+  p.n_tiles = static_cast<int>(pair_n_tiles);
+  p.columns_fastest = 1;
+  const int pairs = static_cast<int>(m_pairs * pair_n_tiles);
+  return pair_bn == 256 ? launch_pair_bn<256, 4, false, true>(map_a, map_p, p, pairs, stream)
+                        : launch_pair_bn<192, 4, false, true>(map_a, map_p, p, pairs, stream);
 }
 
 // Name of the large-row kernel this problem gets (for reports; launches nothing).

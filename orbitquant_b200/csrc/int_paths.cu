@@ -70,6 +70,37 @@ expand_packed_a4_kernel(const uint8_t *packed_act, const float *token_norms, con
   }
 }
 
+// packed_act [rows, dim/2] (low nibble = even k) -> out [rows, dim] INT8 code table entries (the
+// operand of the kind::i8 tensor-core GEMM); row_scale[m] = token_norms[m] * scale.
+__global__ void __launch_bounds__(kExpandThreads)
+expand_packed_a4_int8_kernel(const uint8_t *packed_act, const float *token_norms, const int8_t *act_codes,
+                             float scale, int64_t rows, int64_t dim, int8_t *out, float *row_scale) {
+  __shared__ uint16_t s_pair[256];   // byte -> the two code-table bytes of its nibbles
+  for (int i = threadIdx.x; i < 256; i += kExpandThreads) {
+    s_pair[i] = static_cast<uint16_t>(static_cast<uint8_t>(act_codes[i & 15])) |
+                static_cast<uint16_t>(static_cast<uint16_t>(static_cast<uint8_t>(act_codes[i >> 4])) << 8);
+  }
+  __syncthreads();
+  const int64_t vectors = rows * (dim / 2) / 8;   // 8 packed bytes -> 16 values
+  for (int64_t v = blockIdx.x * static_cast<int64_t>(kExpandThreads) + threadIdx.x; v < vectors;
+       v += static_cast<int64_t>(gridDim.x) * kExpandThreads) {
+    const uint2 in = __ldg(reinterpret_cast<const uint2 *>(packed_act) + v);
+    const uint32_t w[2] = {in.x, in.y};
+    uint32_t o[4];
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+      const uint32_t lo = s_pair[(w[q >> 1] >> (16 * (q & 1))) & 0xffu];
+      const uint32_t hi = s_pair[(w[q >> 1] >> (16 * (q & 1) + 8)) & 0xffu];
+      o[q] = lo | (hi << 16);
+    }
+    reinterpret_cast<uint4 *>(out)[v] = make_uint4(o[0], o[1], o[2], o[3]);
+  }
+  for (int64_t m = blockIdx.x * static_cast<int64_t>(kExpandThreads) + threadIdx.x; m < rows;
+       m += static_cast<int64_t>(gridDim.x) * kExpandThreads) {
+    row_scale[m] = __fmul_rn(token_norms[m], scale);
+  }
+}
+
 // ---- exact pair-product table ----
 constexpr int kLutThreads = 256;
 constexpr int kLutCols = 64;      // output features per CTA
@@ -174,6 +205,25 @@ int launch_expand_packed_a4(const uint8_t *packed_act, const float *token_norms,
   OQ_CHECK_CUDA(cudaGetLastError());
   expand_packed_a4_kernel<<<grid > 0 ? grid : 1, kExpandThreads, 0, stream>>>(
       packed_act, token_norms, act_codes, scale, rows, dim, static_cast<__half *>(out_f16), row_scale);
+  OQ_CHECK_CUDA(cudaGetLastError());
+  count_launch(2);
+  return OQ_OK;
+}
+
+// As launch_expand_packed_a4, with an INT8 operand [rows, dim] for the kind::i8 GEMM.
+int launch_expand_packed_a4_int8(const uint8_t *packed_act, const float *token_norms, const int8_t *act_codes,
+                                 const int8_t *w_codes, int w_levels, float scale, int64_t rows, int64_t dim,
+                                 void *out_int8, float *row_scale, float *table_scale, float *w_code_floats,
+                                 cudaStream_t stream) {
+  OQ_CHECK_ARG(dim % 16 == 0, "in_features must be a multiple of 16");
+  OQ_CHECK_ARG(aligned16(out_int8) && (reinterpret_cast<uintptr_t>(packed_act) & 7u) == 0,
+               "packed activations must be 8-byte aligned, the operand 16-byte aligned");
+  const int64_t vectors = rows * dim / 16;
+  const unsigned grid = static_cast<unsigned>(std::min<int64_t>((vectors + kExpandThreads - 1) / kExpandThreads, 148 * 16));
+  write_code_table_kernel<<<1, 256, 0, stream>>>(w_codes, w_levels, table_scale, w_code_floats);
+  OQ_CHECK_CUDA(cudaGetLastError());
+  expand_packed_a4_int8_kernel<<<grid > 0 ? grid : 1, kExpandThreads, 0, stream>>>(
+      packed_act, token_norms, act_codes, scale, rows, dim, static_cast<int8_t *>(out_int8), row_scale);
   OQ_CHECK_CUDA(cudaGetLastError());
   count_launch(2);
   return OQ_OK;

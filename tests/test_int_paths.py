@@ -174,3 +174,43 @@ def test_pair_lut_module_mode_matches_exact_forward(oracle):
         pair_lut=lut, out_features=130)
     assert torch.equal(bits_of(got), bits_of(ref))
     assert rel_l2(got.float(), exact.float()) <= 5e-3
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("rows,k,n", [(300, 1024, 384), (1100, 768, 840), (2048, 3072, 1024)])
+def test_int8_surrogate_matmul_on_int8_tensor_cores(oracle, rows, k, n):
+    """Above 128 rows a W4 layer with in_features % 128 == 0 contracts INT8 operands
+    (tcgen05.mma kind::i8, int32 accumulation): the integers of the reference's INT8 kernels.
+    The same layer through the f16 route (INT8 codes are exact in f16, the fp32 accumulator exact
+    below 2^24) must give the same bits."""
+    from orbitquant_b200 import native
+    dev = _dev()
+    torch.manual_seed(rows + n)
+    cfg = OrbitQuantConfig(weight_bits=4, activation_bits=4, rotation_seed=3)
+    lin = torch.nn.Linear(k, n)
+    with torch.no_grad():
+        lin.weight.mul_(0.02 / lin.weight.std())
+    module = OrbitQuantLinear.from_linear(lin, config=cfg, module_name="i8").to(dev)
+    module.weight_mode = "int8_surrogate"
+    x = torch.randn(rows, k)
+    x[:, :4] *= 15
+    x = x.to(torch.bfloat16).to(dev)
+    native.gemm_clear_device_status()
+    try:
+        native.set_tunable("int8_mma", 0)
+        via_f16 = module(x)
+        native.set_tunable("int8_mma", None)
+        via_i8 = module(x)
+        torch.cuda.synchronize()
+    finally:
+        native.set_tunable("int8_mma", None)
+    assert native.gemm_device_status() == 0
+    assert torch.equal(via_f16, via_i8)
+    a_codes, a_scale = fit_int8_centroid_surrogate(module.activation_codebook.centroids)
+    w_codes, w_scale = fit_int8_centroid_surrogate(module.weight_codebook.centroids)
+    ref, _ref32 = oracle.int8_surrogate_linear(
+        x.cpu(), module.packed_weight_indices.cpu(), module.row_norms.cpu(), module.bias.detach().cpu(),
+        perm=module.rotation.permutation, signs=module.rotation.signs, block=module.rotation.block_size,
+        act_boundaries=module.activation_codebook.boundaries, act_centroids=module.activation_codebook.centroids,
+        act_codes=a_codes, act_scale=a_scale, w_codes=w_codes, w_scale=w_scale, w_bits=4, out_features=n)
+    assert rel_l2(via_i8.float().cpu(), ref.float()) <= 1e-3
