@@ -183,8 +183,9 @@ def synth_activations(rows, k, seed, outliers="random", device=None):
     return x.to(torch.bfloat16)
 
 
-def build_layers(workload, device, rank=0, world=1, rows_override=0, on_device=False):
-    """[(Layer, module on `device`)] of a workload; column shards when world > 1."""
+def build_layers(workload, device, rank=0, world=1, rows_override=0, on_device=False, weight_mode=None):
+    """[(Layer, module on `device`)] of a workload; column shards when world > 1.  `weight_mode`
+    selects another formulation of the same layers ("int8_surrogate": the integer route)."""
     from orbitquant_b200 import OrbitQuantConfig, OrbitQuantLinear
     from orbitquant_b200.sharding import shard_linear
 
@@ -206,6 +207,8 @@ def build_layers(workload, device, rank=0, world=1, rows_override=0, on_device=F
                                   row_norms=norms.clone(), debug_weight=None)
         if world > 1:
             module = shard_linear(module, rank, world, config=cfg)
+        if weight_mode is not None:
+            module.weight_mode = weight_mode
         layers.append((layer, module.to(device)))
     return (rows_override or spec["rows"]), layers, spec
 
@@ -603,11 +606,12 @@ def kernel_alone(layers, inputs, steps, peaks):
 
 
 def measure_single_gpu(workload, device, steps, warmup, rows_override=0, on_device=False,
-                       with_kernel=True, sustained=True):
+                       with_kernel=True, sustained=True, weight_mode=None):
     """value / ms_per_step of a large-row workload on one GPU, resident inputs."""
     from orbitquant_b200 import native
 
-    rows, layers, spec = build_layers(workload, device, rows_override=rows_override, on_device=on_device)
+    rows, layers, spec = build_layers(workload, device, rows_override=rows_override, on_device=on_device,
+                                      weight_mode=weight_mode)
     # stacked blocks share the input tensors of their (up to six) distinct projections
     distinct = [synth_activations(rows, l.k, spec["seed"] * 1000 + i, spec["outliers"],
                                   device if on_device else None).to(device)
@@ -785,6 +789,25 @@ def main():
                 others[name] = res
             except Exception as exc:
                 others[name] = {"error": f"{type(exc).__name__}: {exc}"}
+        try:
+            # the same four projections through the integer route of the reference's INT8
+            # surrogate: INT8 code operands on the INT8 tensor-core instructions; approximate by
+            # construction, so it is reported beside the headline, never as it
+            res, l_, i_, _s = measure_single_gpu("dit_block", device, extras_steps, 3, on_device=True,
+                                                 sustained=False, with_kernel=False,
+                                                 weight_mode="int8_surrogate")
+            backends = sorted({m.last_activation_kernel_backend for _l, m in l_})
+            del l_, i_
+            torch.cuda.empty_cache()
+            res["unit"] = "T-op/s"
+            res["what"] = ("weight_mode int8_surrogate: rotate + quantise to INT8 codes, "
+                           "tcgen05.mma kind::i8 with int32 accumulation; 2*M*K*N operations per layer")
+            res["backends"] = backends
+            res.pop("frac_of_burst", None)
+            res.pop("frac_of_sustained", None)
+            others["dit_block_int8_surrogate"] = res
+        except Exception as exc:
+            others["dit_block_int8_surrogate"] = {"error": f"{type(exc).__name__}: {exc}"}
         line["configs"] = others
     line["gemm_device_status"] = native.gemm_device_status()
 

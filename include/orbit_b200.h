@@ -225,6 +225,26 @@ int oq_matmul_packed_w4a4_int8(void *out, const uint8_t *packed_act, const uint8
                                int64_t out_features, void *workspace, size_t workspace_bytes,
                                void *stream);
 
+/* The whole INT8-surrogate W4A4 linear in three launches (code table, rotate + quantise
+ * straight to the INT8 operand, INT8 tensor-core GEMM): out = the result of
+ * oq_quantize_activations_packed_w4 followed by oq_matmul_packed_w4a4_int8, without the packed
+ * intermediate.  Replaces the reference module's fused INT8 route
+ * (src/orbitquant/layers.py:1097-1352 calling quantize_activations_int8 and the fused kernels of
+ * src/orbitquant/kernels/triton_cuda.py:1861-2099).  bf16 output.  oq_linear_w4a4_int8_supported
+ * returns 1 for the problems it takes: bf16 x, rows > 128, in_features % 256 == 0, a rotation
+ * block of 256 .. 4096 dividing in_features, 4-bit weights; other problems go through the two
+ * calls above. */
+int oq_linear_w4a4_int8_supported(int dtype, int64_t rows, int64_t in_features, int64_t out_features,
+                                  int64_t block);
+size_t oq_linear_w4a4_int8_workspace_bytes(int64_t rows, int64_t in_features);
+int oq_linear_w4a4_int8(void *out, const void *x, int dtype, int64_t rows, int64_t in_features,
+                        int64_t out_features, const uint8_t *packed_weight, int64_t packed_weight_bytes,
+                        const void *row_norms_bf16, const void *bias, int bias_dtype, const int32_t *perm,
+                        const int8_t *signs, int64_t block, const float *act_boundaries,
+                        const float *act_centroids, const int8_t *act_codes, const int8_t *weight_codes,
+                        float act_scale, float weight_scale, float eps, void *workspace,
+                        size_t workspace_bytes, void *stream);
+
 /* Exact W4A4 linear through the 256-entry pair-product table:
  *   out[m, n] = (sum_k pair_lut[16 * a[m,k] + w[n,k]]) * token_norm[m] * row_norm[n] + bias[n]
  * in fp32, rounded to x's dtype, pair_lut[16 i + j] = act_centroid[i] * weight_centroid[j].

@@ -59,6 +59,14 @@ int launch_expand_packed_a4_int8(const uint8_t *packed_act, const float *token_n
                                  const int8_t *w_codes, int w_levels, float scale, int64_t rows, int64_t dim,
                                  void *out_int8, float *row_scale, float *table_scale, float *w_code_floats,
                                  cudaStream_t stream);
+int launch_write_code_table(const int8_t *w_codes, int w_levels, float *table_scale, float *w_code_floats,
+                            cudaStream_t stream);
+bool int8_operand_prologue_supported(int x_dtype, int64_t dim, int64_t block);
+int launch_rotate_quantize_int8_operand(const void *x, int x_dtype, int64_t rows, int64_t dim,
+                                        const int32_t *perm, const int8_t *signs, int64_t block,
+                                        const float *boundaries, const float *centroids, int bits, float eps,
+                                        const int8_t *code_map, float out_scale, int8_t *out,
+                                        float *row_scale, cudaStream_t stream);
 int launch_expand_packed_a4(const uint8_t *packed_act, const float *token_norms, const int8_t *act_codes,
                             const int8_t *w_codes, int w_levels, float scale, int64_t rows, int64_t dim,
                             void *out_f16, float *row_scale, float *table_scale, float *w_code_floats,
@@ -462,6 +470,63 @@ int oq_matmul_packed_w4a4_int8(void *out, const uint8_t *packed_act, const uint8
   // token_norm * s_a * s_w, so the ordinary epilogue computes the surrogate's
   return launch_tcgen05_gemm(out, workspace, row_scale, table_scale, rows, in_features, out_features,
                              packed_weight, weight_bits, row_norms_bf16, code_floats, bias, bias_dtype, s);
+}
+
+int oq_linear_w4a4_int8_supported(int dtype, int64_t rows, int64_t in_features, int64_t out_features,
+                                  int64_t block) {
+  return tcgen05_i8_supported(rows, in_features, out_features, 4) &&
+                 int8_operand_prologue_supported(dtype, in_features, block) && tunable(OQ_TUNE_INT8_MMA) != 0
+             ? 1
+             : 0;
+}
+
+size_t oq_linear_w4a4_int8_workspace_bytes(int64_t rows, int64_t in_features) {
+  return oq_matmul_packed_w4a4_int8_workspace_bytes(rows, in_features);
+}
+
+int oq_linear_w4a4_int8(void *out, const void *x, int dtype, int64_t rows, int64_t in_features,
+                        int64_t out_features, const uint8_t *packed_weight, int64_t packed_weight_bytes,
+                        const void *row_norms_bf16, const void *bias, int bias_dtype, const int32_t *perm,
+                        const int8_t *signs, int64_t block, const float *act_boundaries,
+                        const float *act_centroids, const int8_t *act_codes, const int8_t *weight_codes,
+                        float act_scale, float weight_scale, float eps, void *workspace,
+                        size_t workspace_bytes, void *stream) {
+  OQ_CHECK_ARG(rows >= 0 && in_features > 0 && out_features >= 0, "negative or empty shape");
+  OQ_CHECK_ARG(bias == nullptr || valid_dtype(bias_dtype), "bias must be float32, float16, or bfloat16");
+  OQ_CHECK_ARG(packed_weight_bytes >= (out_features * in_features * 4 + 7) / 8, "packed weights are too short");
+  if (rows == 0 || out_features == 0) {
+    return OQ_OK;
+  }
+  OQ_CHECK_ARG(out && x && packed_weight && row_norms_bf16 && act_codes && weight_codes, "null device pointer");
+  if (!oq_linear_w4a4_int8_supported(dtype, rows, in_features, out_features, block)) {
+    return fail(OQ_ERR_UNSUPPORTED,
+                "the fused INT8-surrogate linear takes bf16 rows, more than 128 of them, in_features %% 256 == 0 "
+                "and a rotation block of 256 .. 4096");
+  }
+  const size_t need = oq_linear_w4a4_int8_workspace_bytes(rows, in_features);
+  if (workspace == nullptr || workspace_bytes < need) {
+    return fail(OQ_ERR_WORKSPACE, "workspace of %zu bytes given, %zu needed", workspace_bytes, need);
+  }
+  OQ_CHECK_ARG(aligned16(workspace), "workspace must be 16-byte aligned");
+  if (int rc = check_device()) {
+    return rc;
+  }
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  unsigned char *ws = static_cast<unsigned char *>(workspace);
+  float *row_scale = reinterpret_cast<float *>(ws + f16_operand_bytes(rows, in_features));
+  float *table_scale = row_scale + rows;
+  float *code_floats = reinterpret_cast<float *>(ws + tcgen05_head_bytes(rows, in_features));
+  if (int rc = launch_write_code_table(weight_codes, 16, table_scale, code_floats, s)) {
+    return rc;
+  }
+  if (int rc = launch_rotate_quantize_int8_operand(x, dtype, rows, in_features, perm, signs, block,
+                                                   act_boundaries, act_centroids, 4, eps, act_codes,
+                                                   act_scale * weight_scale, reinterpret_cast<int8_t *>(ws),
+                                                   row_scale, s)) {
+    return rc == OQ_ERR_UNSUPPORTED ? fail(rc, "the INT8-operand prologue does not take this problem") : rc;
+  }
+  return launch_tcgen05_gemm_i8(out, workspace, row_scale, table_scale, rows, in_features, out_features,
+                                packed_weight, row_norms_bf16, code_floats, bias, bias_dtype, s);
 }
 
 size_t oq_linear_w4a4_pair_lut_workspace_bytes(int64_t rows, int64_t in_features) {

@@ -211,6 +211,16 @@ int launch_expand_packed_a4(const uint8_t *packed_act, const float *token_norms,
 }
 
 // As launch_expand_packed_a4, with an INT8 operand [rows, dim] for the kind::i8 GEMM.
+// The weight code table as floats (what the GEMM's operand expansion reads) and a table scale
+// of 1, for callers that produce the INT8 activation operand themselves.
+int launch_write_code_table(const int8_t *w_codes, int w_levels, float *table_scale, float *w_code_floats,
+                            cudaStream_t stream) {
+  write_code_table_kernel<<<1, 256, 0, stream>>>(w_codes, w_levels, table_scale, w_code_floats);
+  OQ_CHECK_CUDA(cudaGetLastError());
+  count_launch();
+  return OQ_OK;
+}
+
 int launch_expand_packed_a4_int8(const uint8_t *packed_act, const float *token_norms, const int8_t *act_codes,
                                  const int8_t *w_codes, int w_levels, float scale, int64_t rows, int64_t dim,
                                  void *out_int8, float *row_scale, float *table_scale, float *w_code_floats,

@@ -531,6 +531,84 @@ size_t prologue_smem_bytes(int dim, int rows_per_cta, int dtype) {
 // Blocks of any power of two up to the dim limit: 256 (warp) x 16 per register pass.
 constexpr int64_t kMaxBlock = 1 << 20;
 
+bool int8_operand_prologue_supported(int x_dtype, int64_t dim, int64_t block) {
+  return block > 0 && dim % block == 0 && warp_prologue_supported(x_dtype, dim, block, 4);
+}
+
+// The INT8 activation operand of the INT8 tensor-core GEMM in one pass: out[m, k] =
+// code_map[level of element k of token m] (one byte), row_scale[m] = token norm * out_scale.  The
+// warp-per-block kernel only (bf16 rows, dim % 256 == 0, block 256 .. 4096); OQ_ERR_UNSUPPORTED
+// otherwise, and the caller takes the general kernel's code output instead.
+int launch_rotate_quantize_int8_operand(const void *x, int x_dtype, int64_t rows, int64_t dim,
+                                        const int32_t *perm, const int8_t *signs, int64_t block,
+                                        const float *boundaries, const float *centroids, int bits, float eps,
+                                        const int8_t *code_map, float out_scale, int8_t *out,
+                                        float *row_scale, cudaStream_t stream) {
+  if (!(bits == 4 && rows > 0 && int8_operand_prologue_supported(x_dtype, dim, block))) {
+    return OQ_ERR_UNSUPPORTED;
+  }
+  OQ_CHECK_ARG(x != nullptr && perm != nullptr && signs != nullptr && boundaries != nullptr &&
+                   centroids != nullptr && code_map != nullptr && out != nullptr && row_scale != nullptr,
+               "null device pointer");
+  OQ_CHECK_ARG(aligned16(x) && aligned16(out) && aligned16(perm) &&
+                   (reinterpret_cast<uintptr_t>(signs) & 7u) == 0,
+               "x, the operand and perm must be 16-byte aligned, signs 8-byte aligned");
+  int device = 0;
+  int sm_count = 0;
+  int max_smem = 0;
+  OQ_CHECK_CUDA(cudaGetDevice(&device));
+  OQ_CHECK_CUDA(cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, device));
+  OQ_CHECK_CUDA(cudaDeviceGetAttribute(&max_smem, cudaDevAttrMaxSharedMemoryPerBlockOptin, device));
+  int batch_rows = 0;
+  int slots = 0;
+  int ctas_per_sm = 0;
+  int smem_bytes = 0;
+  int transform_warps = kPwWarps;
+  if (!plan_warp_prologue(static_cast<int>(dim), static_cast<int>(block), bits, rows, max_smem, &batch_rows,
+                          &slots, &ctas_per_sm, &smem_bytes, &transform_warps)) {
+    return OQ_ERR_UNSUPPORTED;
+  }
+  WarpPrologueParams wp{};
+  wp.x = static_cast<const uint16_t *>(x);
+  wp.xq = reinterpret_cast<uint16_t *>(out);
+  wp.row_scale = row_scale;
+  wp.code_map = code_map;
+  wp.out_scale = out_scale;
+  wp.perm = perm;
+  wp.signs = signs;
+  wp.boundaries = boundaries;
+  wp.centroids = centroids;
+  wp.rows = rows;
+  wp.dim = static_cast<int>(dim);
+  wp.log2_block = 0;
+  while ((int64_t(1) << wp.log2_block) < block) {
+    ++wp.log2_block;
+  }
+  wp.batch_rows = batch_rows;
+  wp.slots = slots;
+  wp.eps = eps;
+  wp.inv_sqrt_block = static_cast<float>(1.0 / sqrt(static_cast<double>(block)));
+  void (*wkernel)(WarpPrologueParams) =
+      transform_warps == kPwWideWarps ? rotate_quantize_warp_kernel<4, false, kPwWideWarps, true>
+                                      : rotate_quantize_warp_kernel<4, false, kPwWarps, true>;
+  OQ_CHECK_CUDA(cudaFuncSetAttribute(wkernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes));
+  const int64_t batches = (rows + batch_rows - 1) / batch_rows;
+  const int wgrid = static_cast<int>(std::min<int64_t>(batches, static_cast<int64_t>(sm_count) * ctas_per_sm));
+  cudaLaunchConfig_t config = {};
+  config.gridDim = dim3(static_cast<unsigned>(wgrid));
+  config.blockDim = dim3(static_cast<unsigned>(pw_threads(transform_warps)));
+  config.dynamicSmemBytes = static_cast<size_t>(smem_bytes);
+  config.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  config.attrs = attr;
+  config.numAttrs = 1;
+  OQ_CHECK_CUDA(cudaLaunchKernelEx(&config, wkernel, wp));
+  count_launch();
+  return OQ_OK;
+}
+
 int launch_rotate_quantize(const void *x, int x_dtype, int64_t rows, int64_t dim,
                            const int32_t *perm, const int8_t *signs, int64_t block,
                            const float *boundaries, const float *centroids, int bits, float eps,

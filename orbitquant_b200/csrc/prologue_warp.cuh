@@ -64,7 +64,9 @@ __host__ __device__ constexpr int pw_max_cells(int bits) {
 struct WarpPrologueParams {
   const uint16_t *x;
   uint16_t *xq;
-  float *row_scale;  // f16 operand mode: per-token factor 2^(E-14)
+  float *row_scale;  // f16 operand mode: per-token factor 2^(E-14); INT8 mode: norm * out_scale
+  const int8_t *code_map;  // INT8 mode: output byte of every quantisation level
+  float out_scale;         // INT8 mode: factor applied to the token norm
   const int32_t *perm;
   const int8_t *signs;
   const float *boundaries;
@@ -147,6 +149,9 @@ __device__ __forceinline__ void pw_sts_f32(uint32_t a, float v) {
 }
 __device__ __forceinline__ void pw_sts_u16(uint32_t a, uint32_t v) {
   asm volatile("st.shared.u16 [%0], %1;" ::"r"(a), "r"(v) : "memory");   // low halfword of v
+}
+__device__ __forceinline__ void pw_sts_u8(uint32_t a, uint32_t v) {
+  asm volatile("st.shared.u8 [%0], %1;" ::"r"(a), "r"(v) : "memory");    // low byte of v
 }
 
 __device__ __forceinline__ void pw_mbar_init(uint32_t bar, uint32_t count) {
@@ -322,7 +327,7 @@ __device__ __forceinline__ void pw_quantize_all(float (&w)[N], const PwQuant &q)
 
 // Pass B of one chunk (and, for blocks up to 1024, the quantisation): lane b owns column b of
 // the 32 x 32 arrangement held in the warp's scratch.
-template <int BITS, bool CELLS, int STAGES, bool FINAL>
+template <int BITS, bool CELLS, int STAGES, bool FINAL, bool OUT8 = false>
 __device__ __forceinline__ void pw_pass_b(uint32_t scratch, uint32_t result, int lane, int active_rows,
                                           const PwQuant &q) {
   float w[32];
@@ -339,17 +344,26 @@ __device__ __forceinline__ void pw_pass_b(uint32_t scratch, uint32_t result, int
       pw_bulk_store_wait_read();   // the previous chunk's results have left the staging area
     }
     __syncwarp();
-    const uint32_t dst = result + lane * 2;
+    // results in position order: 16-bit values, or (OUT8) bytes
+    const uint32_t dst = result + lane * (OUT8 ? 1 : 2);
     if (active_rows == 32) {
 #pragma unroll
       for (int a = 0; a < 32; ++a) {
-        pw_sts_u16(dst + a * 64, __float_as_uint(w[a]));
+        if (OUT8) {
+          pw_sts_u8(dst + a * 32, __float_as_uint(w[a]));
+        } else {
+          pw_sts_u16(dst + a * 64, __float_as_uint(w[a]));
+        }
       }
     } else {
 #pragma unroll
       for (int a = 0; a < 32; ++a) {
         if (a < active_rows) {
-          pw_sts_u16(dst + a * 64, __float_as_uint(w[a]));
+          if (OUT8) {
+            pw_sts_u8(dst + a * 32, __float_as_uint(w[a]));
+          } else {
+            pw_sts_u16(dst + a * 64, __float_as_uint(w[a]));
+          }
         }
       }
     }
@@ -365,7 +379,7 @@ __device__ __forceinline__ void pw_pass_b(uint32_t scratch, uint32_t result, int
 
 // Pass C of a team block: widths 1024 (and 2048) across the team's TEAM chunks, then the
 // quantisation.  Thread tt of the team owns positions tt, tt + threads, ...
-template <int BITS, bool CELLS, int TEAM>
+template <int BITS, bool CELLS, int TEAM, bool OUT8 = false>
 __device__ __forceinline__ void pw_pass_c(uint32_t scratch, uint32_t result, int tt, const PwQuant &q) {
   constexpr int kThreads = TEAM * 32;
   constexpr int kPer = kPwChunk / kThreads;   // positions per thread: 16 (two chunks) or 8 (four)
@@ -390,15 +404,23 @@ __device__ __forceinline__ void pw_pass_c(uint32_t scratch, uint32_t result, int
     for (int i = 0; i < kBatch; ++i) {
 #pragma unroll
       for (int t = 0; t < TEAM; ++t) {
-        pw_sts_u16(result + (t * kPwChunk + tt + kThreads * (i0 + i)) * 2, __float_as_uint(c[i][t]));
+        if (OUT8) {
+          pw_sts_u8(result + (t * kPwChunk + tt + kThreads * (i0 + i)), __float_as_uint(c[i][t]));
+        } else {
+          pw_sts_u16(result + (t * kPwChunk + tt + kThreads * (i0 + i)) * 2, __float_as_uint(c[i][t]));
+        }
       }
     }
   }
 }
 
-template <int BITS, bool F16OP, int TW = kPwWarps>
+// F16OP: output = the f16 operand of the tensor-core GEMM (+ per-token factor).  OUT8: output =
+// one byte per element, the INT8 code `code_map[level]` (+ per-token factor norm * out_scale),
+// the operand of the INT8 tensor-core GEMM.  Neither: x_q in bf16.
+template <int BITS, bool F16OP, int TW = kPwWarps, bool OUT8 = false>
 __global__ void __launch_bounds__(pw_threads(TW), (TW == kPwWarps ? 2 : 1))
 rotate_quantize_warp_kernel(const WarpPrologueParams p) {
+  static_assert(!(F16OP && OUT8), "one output format");
   constexpr int kPwThreads = pw_threads(TW);
 
   extern __shared__ unsigned char pw_smem_raw[];
@@ -669,6 +691,8 @@ rotate_quantize_warp_kernel(const WarpPrologueParams p) {
             back = ldexpf(1.0f, e - 14);
           }
           p.row_scale[row0 + r] = back;
+        } else if (OUT8) {
+          p.row_scale[row0 + r] = __fmul_rn(norm, p.out_scale);
         }
         meta[0] = norm;
         meta[1] = __fdiv_rn(1.0f, __fadd_rn(norm, p.eps));
@@ -682,8 +706,9 @@ rotate_quantize_warp_kernel(const WarpPrologueParams p) {
         const float *m = s_slot_meta + (slot * kPwMaxRows + rr) * 4;
         const float q = __fmul_rn(s_cent[i & (kLevels - 1)], m[0]);
         const __nv_bfloat16 qb = __float2bfloat16_rn(q);
-        outtab[i] = F16OP ? __half_as_ushort(__float2half_rn(__fmul_rn(__bfloat162float(qb), m[2])))
-                          : __bfloat16_as_ushort(qb);
+        outtab[i] = OUT8 ? static_cast<uint16_t>(static_cast<uint8_t>(p.code_map[i & (kLevels - 1)]))
+                         : (F16OP ? __half_as_ushort(__float2half_rn(__fmul_rn(__bfloat162float(qb), m[2])))
+                                  : __bfloat16_as_ushort(qb));
       }
       __syncwarp();
       if (use_cells) {
@@ -792,21 +817,26 @@ rotate_quantize_warp_kernel(const WarpPrologueParams p) {
         // ---- pass B with the quantisation; widths up to the block ----
         if (use_cells) {
           switch (p.log2_block) {
-            case 8: pw_pass_b<BITS, true, 3, true>(my_scratch, result, lane, active_lanes, quant); break;
-            case 9: pw_pass_b<BITS, true, 4, true>(my_scratch, result, lane, active_lanes, quant); break;
-            default: pw_pass_b<BITS, true, 5, true>(my_scratch, result, lane, active_lanes, quant); break;
+            case 8: pw_pass_b<BITS, true, 3, true, OUT8>(my_scratch, result, lane, active_lanes, quant); break;
+            case 9: pw_pass_b<BITS, true, 4, true, OUT8>(my_scratch, result, lane, active_lanes, quant); break;
+            default: pw_pass_b<BITS, true, 5, true, OUT8>(my_scratch, result, lane, active_lanes, quant); break;
           }
         } else {
           switch (p.log2_block) {
-            case 8: pw_pass_b<BITS, false, 3, true>(my_scratch, result, lane, active_lanes, quant); break;
-            case 9: pw_pass_b<BITS, false, 4, true>(my_scratch, result, lane, active_lanes, quant); break;
-            default: pw_pass_b<BITS, false, 5, true>(my_scratch, result, lane, active_lanes, quant); break;
+            case 8: pw_pass_b<BITS, false, 3, true, OUT8>(my_scratch, result, lane, active_lanes, quant); break;
+            case 9: pw_pass_b<BITS, false, 4, true, OUT8>(my_scratch, result, lane, active_lanes, quant); break;
+            default: pw_pass_b<BITS, false, 5, true, OUT8>(my_scratch, result, lane, active_lanes, quant); break;
           }
         }
         pw_fence_async();
         __syncwarp();
         if (lane == 0) {
-          pw_bulk_store(p.xq + (row0 + r) * dim + chunk_first, result, static_cast<uint32_t>(chunk_len) * 2);
+          if (OUT8) {
+            pw_bulk_store(reinterpret_cast<uint8_t *>(p.xq) + (row0 + r) * dim + chunk_first, result,
+                          static_cast<uint32_t>(chunk_len));
+          } else {
+            pw_bulk_store(p.xq + (row0 + r) * dim + chunk_first, result, static_cast<uint32_t>(chunk_len) * 2);
+          }
         }
       } else {
         // ---- pass B (widths 32 .. 512) back into the scratch, then pass C across the team ----
@@ -817,20 +847,25 @@ rotate_quantize_warp_kernel(const WarpPrologueParams p) {
         pw_team_barrier(team, team_threads);
         if (use_cells) {
           if (team_size == 2) {
-            pw_pass_c<BITS, true, 2>(scratch, result, tt, quant);
+            pw_pass_c<BITS, true, 2, OUT8>(scratch, result, tt, quant);
           } else {
-            pw_pass_c<BITS, true, 4>(scratch, result, tt, quant);
+            pw_pass_c<BITS, true, 4, OUT8>(scratch, result, tt, quant);
           }
         } else if (team_size == 2) {
-          pw_pass_c<BITS, false, 2>(scratch, result, tt, quant);
+          pw_pass_c<BITS, false, 2, OUT8>(scratch, result, tt, quant);
         } else {
-          pw_pass_c<BITS, false, 4>(scratch, result, tt, quant);
+          pw_pass_c<BITS, false, 4, OUT8>(scratch, result, tt, quant);
         }
         pw_fence_async();
         pw_team_barrier(team, team_threads);   // results complete; scratch free for the next unit
         if (tt == 0) {
-          pw_bulk_store(p.xq + (row0 + r) * dim + static_cast<int64_t>(u) * block, result,
-                        static_cast<uint32_t>(block) * 2);
+          if (OUT8) {
+            pw_bulk_store(reinterpret_cast<uint8_t *>(p.xq) + (row0 + r) * dim + static_cast<int64_t>(u) * block,
+                          result, static_cast<uint32_t>(block));
+          } else {
+            pw_bulk_store(p.xq + (row0 + r) * dim + static_cast<int64_t>(u) * block, result,
+                          static_cast<uint32_t>(block) * 2);
+          }
         }
       }
     }

@@ -364,6 +364,18 @@ class OrbitQuantLinear(nn.Module):
             raise ValueError("the INT8 surrogate path takes 4-bit activations and 2/3/4/6-bit weights")
         device = x.device
         a_codes, a_scale, w_codes, w_scale = self._int8_surrogate_constants(device)
+        if native.linear_w4a4_int8_supported(x, self.in_features, self.out_features,
+                                             self.rotation.block_size, self.weight_bits):
+            self.last_activation_kernel_backend = "orbit_b200_int8_surrogate_fused"
+            y = native.linear_w4a4_int8(
+                x, self.packed_weight_indices, self._row_norms_for(device), self._bias_for(device),
+                permutation=self._rotation_permutation, signs=self._rotation_signs,
+                block_size=self.rotation.block_size,
+                act_boundaries=self._activation_codebook_boundaries,
+                act_centroids=self._activation_codebook_centroids, act_codes=a_codes,
+                weight_codes=w_codes, act_scale=a_scale, weight_scale=w_scale,
+                out_features=self.out_features, eps=self.activation_eps)
+            return y if y.dtype == x.dtype else y.to(x.dtype)
         packed_x, token_norms = native.quantize_activations_packed_w4(
             x, self._rotation_permutation, self._rotation_signs, self._activation_codebook_centroids,
             self._activation_codebook_boundaries, eps=self.activation_eps,

@@ -42,6 +42,10 @@ _SIGNATURES = {
     "oq_quantize_activations_int8": (_int, [_vp, _int, _i64, _i64, _vp, _vp, _i64, _vp, _vp, _int, _vp,
                                             _f32, _vp, _vp, _vp]),
     "oq_matmul_packed_w4a4_int8_workspace_bytes": (_sz, [_i64, _i64]),
+    "oq_linear_w4a4_int8_supported": (_int, [_int, _i64, _i64, _i64, _i64]),
+    "oq_linear_w4a4_int8_workspace_bytes": (_sz, [_i64, _i64]),
+    "oq_linear_w4a4_int8": (_int, [_vp, _vp, _int, _i64, _i64, _i64, _vp, _i64, _vp, _vp, _int, _vp, _vp, _i64,
+                                   _vp, _vp, _vp, _vp, _f32, _f32, _f32, _vp, _sz, _vp]),
     "oq_matmul_packed_w4a4_int8": (_int, [_vp, _vp, _vp, _i64, _int, _vp, _vp, _vp, _vp, _vp, _int, _f32,
                                           _f32, _i64, _i64, _i64, _vp, _sz, _vp]),
     "oq_linear_w4a4_pair_lut_workspace_bytes": (_sz, [_i64, _i64]),
@@ -521,6 +525,47 @@ def matmul_packed_w4a4_int8(packed_act, packed_weight, token_norms, row_norms, a
             float(act_scale), float(weight_scale), rows, in_features, out_features, _ptr(ws), ws_bytes,
             _stream(device)))
     return out.reshape(*packed_act.shape[:-1], out_features)
+
+
+def linear_w4a4_int8_supported(x, in_features, out_features, block_size, weight_bits=4):
+    """Whether ``linear_w4a4_int8`` takes this problem (bf16 rows, more than 128 of them, 4-bit
+    weights, ``in_features % 256 == 0``, rotation block 256 .. 4096)."""
+    if weight_bits != 4 or x.dtype not in DTYPE_CODES or not x.is_cuda:
+        return False
+    rows = x.numel() // max(in_features, 1)
+    return bool(load().oq_linear_w4a4_int8_supported(
+        DTYPE_CODES[x.dtype], rows, int(in_features), int(out_features), int(block_size)))
+
+
+def linear_w4a4_int8(x, packed_weight, row_norms, bias, *, permutation, signs, block_size, act_boundaries,
+                     act_centroids, act_codes, weight_codes, act_scale, weight_scale, out_features, eps):
+    """The INT8-surrogate W4A4 linear in one call: rotate + quantise straight to the INT8 operand,
+    INT8 tensor-core matmul (the reference module's fused INT8 route, ``layers.py:1097-1352``);
+    bf16 output equal to ``quantize_activations_packed_w4`` + ``matmul_packed_w4a4_int8``."""
+    _require_cuda("x", x)
+    in_features = x.shape[-1]
+    device = x.device
+    values = x.contiguous().reshape(-1, in_features)
+    rows = values.shape[0]
+    perm, sgn, cent, bnd = _activation_constants(x, permutation, signs, act_centroids, act_boundaries)
+    pw = packed_weight.to(device=device, dtype=torch.uint8).contiguous()
+    rn = row_norms.to(device=device, dtype=torch.bfloat16).contiguous()
+    ac = act_codes.to(device=device, dtype=torch.int8).contiguous()
+    wc = weight_codes.to(device=device, dtype=torch.int8).contiguous()
+    bias_t = None if bias is None else bias.to(device=device).contiguous()
+    if bias_t is not None and bias_t.dtype not in DTYPE_CODES:
+        bias_t = bias_t.to(torch.float32)
+    out = torch.empty((rows, out_features), dtype=torch.bfloat16, device=device)
+    lib = load()
+    ws_bytes = lib.oq_linear_w4a4_int8_workspace_bytes(rows, in_features)
+    ws = torch.empty(max(ws_bytes, 16), dtype=torch.uint8, device=device)
+    with torch.cuda.device(device):
+        _check(lib.oq_linear_w4a4_int8(
+            _ptr(out), _ptr(values), DTYPE_CODES[x.dtype], rows, in_features, out_features, _ptr(pw),
+            pw.numel(), _ptr(rn), _ptr(bias_t), 0 if bias_t is None else DTYPE_CODES[bias_t.dtype],
+            _ptr(perm), _ptr(sgn), int(block_size), _ptr(bnd), _ptr(cent), _ptr(ac), _ptr(wc),
+            float(act_scale), float(weight_scale), float(eps), _ptr(ws), ws_bytes, _stream(device)))
+    return out.reshape(*x.shape[:-1], out_features)
 
 
 def linear_w4a4_pair_lut(x, packed, row_norms, bias, *, permutation, signs, block_size, act_boundaries,

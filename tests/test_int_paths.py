@@ -214,3 +214,58 @@ def test_int8_surrogate_matmul_on_int8_tensor_cores(oracle, rows, k, n):
         act_boundaries=module.activation_codebook.boundaries, act_centroids=module.activation_codebook.centroids,
         act_codes=a_codes, act_scale=a_scale, w_codes=w_codes, w_scale=w_scale, w_bits=4, out_features=n)
     assert rel_l2(via_i8.float().cpu(), ref.float()) <= 1e-3
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("rows,k,n,block", [(129, 256, 136, 256), (777, 1536, 520, 512), (1500, 2048, 384, 2048),
+                                            (515, 4096, 264, 4096), (2048, 3072, 1024, None)])
+def test_int8_surrogate_fused_linear_equals_the_two_calls(rows, k, n, block):
+    """The fused INT8-surrogate linear (rotate + quantise straight to the INT8 operand, then the
+    INT8 tensor-core matmul) against the packed-activation route it shortens
+    (quantize_activations_packed_w4 + matmul_packed_w4a4_int8): same indices, same integers, same
+    per-token factor, hence the same bits -- for every rotation block the prologue covers,
+    including the blocks two and four warps share."""
+    from orbitquant_b200 import native
+    dev = _dev()
+    torch.manual_seed(rows * 3 + n)
+    kwargs = {} if block is None else {"block_size": block}
+    cfg = OrbitQuantConfig(weight_bits=4, activation_bits=4, rotation_seed=11, **kwargs)
+    lin = torch.nn.Linear(k, n)
+    with torch.no_grad():
+        lin.weight.mul_(0.02 / lin.weight.std())
+    module = OrbitQuantLinear.from_linear(lin, config=cfg, module_name="i8f").to(dev)
+    module.weight_mode = "int8_surrogate"
+    x = torch.randn(rows, k)
+    x[:, :4] *= 15
+    x[rows // 2] = 0          # a zero token: norm clamps to eps, codes are the middle level
+    x = x.to(torch.bfloat16).to(dev)
+    assert native.linear_w4a4_int8_supported(x, k, n, module.rotation.block_size)
+    native.gemm_clear_device_status()
+    fused = module(x)
+    assert module.last_activation_kernel_backend == "orbit_b200_int8_surrogate_fused"
+    a_codes, a_scale, w_codes, w_scale = module._int8_surrogate_constants(dev)
+    packed_x, token_norms = native.quantize_activations_packed_w4(
+        x, module._rotation_permutation, module._rotation_signs, module._activation_codebook_centroids,
+        module._activation_codebook_boundaries, eps=module.activation_eps,
+        block_size=module.rotation.block_size)
+    two_calls = native.matmul_packed_w4a4_int8(
+        packed_x, module.packed_weight_indices, token_norms, module._row_norms_for(dev), a_codes, w_codes,
+        act_scale=a_scale, weight_scale=w_scale, out_features=n, in_features=k, weight_bits=4,
+        bias=module._bias_for(dev))
+    torch.cuda.synchronize()
+    assert native.gemm_device_status() == 0
+    assert torch.equal(fused, two_calls)
+
+
+@pytest.mark.gpu
+def test_int8_surrogate_fused_linear_declines_what_it_does_not_cover():
+    from orbitquant_b200 import native
+    dev = _dev()
+    x = torch.zeros(64, 1024, dtype=torch.bfloat16, device=dev)
+    assert not native.linear_w4a4_int8_supported(x, 1024, 256, 1024)          # few rows: other kernels
+    x = torch.zeros(512, 1024, dtype=torch.float16, device=dev)
+    assert not native.linear_w4a4_int8_supported(x, 1024, 256, 1024)          # f16 rows
+    x = torch.zeros(512, 1024, dtype=torch.bfloat16, device=dev)
+    assert not native.linear_w4a4_int8_supported(x, 1024, 256, 128)           # narrow rotation block
+    assert not native.linear_w4a4_int8_supported(x, 1024, 256, 1024, weight_bits=2)
+    assert native.linear_w4a4_int8_supported(x, 1024, 256, 1024)
