@@ -81,7 +81,8 @@ uint64_t oq_launch_count(void);
  * (128|192|256), tile_order (0|1), skinny (0|1), stream_rows (0|1), prologue_rows (1..8),
  * skinny_units_per_sm, skinny_min_iters, fused_decode (0|1), prologue_kernel (0|1|2),
  * pair (0 = never the CTA-pair kernel, 1 = always, 192|256 = always with that tile width),
- * int8_mma (0 = the INT8-surrogate matmul never uses INT8 tensor-core instructions).
+ * int8_mma (0 = the INT8-surrogate matmul never uses INT8 tensor-core instructions),
+ * gemv (0 = one to four tokens never take the CUDA-core GEMV, 1 = wherever it is supported).
  * Process-wide and not synchronised with launches in flight on other threads. */
 int oq_set_tunable(const char *name, int value);
 

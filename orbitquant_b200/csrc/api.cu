@@ -14,7 +14,7 @@ std::atomic<uint64_t> g_launch_count{0};
 namespace {
 const char *const kTunableNames[OQ_TUNE_COUNT] = {
     "TILE_N", "TILE_ORDER", "SKINNY", "STREAM_ROWS", "PROLOGUE_ROWS", "SKINNY_UNITS_PER_SM",
-    "SKINNY_MIN_ITERS", "FUSED_DECODE", "PROLOGUE_KERNEL", "PAIR", "INT8_MMA"};
+    "SKINNY_MIN_ITERS", "FUSED_DECODE", "PROLOGUE_KERNEL", "PAIR", "INT8_MMA", "GEMV"};
 std::atomic<int> g_tunables[OQ_TUNE_COUNT];
 std::once_flag g_tunables_once;
 
@@ -133,6 +133,11 @@ int launch_tcgen05_rtn_int4(void *out, const void *x_bf16, int64_t rows, int64_t
                             int64_t out_features, const uint8_t *packed, const void *scales_bf16,
                             const void *bias, int bias_dtype, void *workspace,
                             size_t workspace_bytes, cudaStream_t stream);
+bool gemv_w4_supported(int64_t rows, int64_t in_features, int64_t out_features, int bits, int dtype,
+                       int weight_mode);
+int launch_gemv_w4(void *out, const void *x, int64_t rows, int64_t in_features, int64_t out_features,
+                   const uint8_t *packed, const void *row_norms_bf16, const float *centroids,
+                   const void *bias, int bias_dtype, cudaStream_t stream);
 bool decode_fused_supported(int64_t rows, int64_t in_features, int64_t out_features, int weight_bits,
                             int act_bits, int dtype, int64_t block);
 int launch_decode_fused(void *out, const void *x, int64_t rows, int64_t in_features, int64_t out_features,
@@ -179,11 +184,25 @@ bool use_skinny(int64_t rows, int64_t in_features, int64_t out_features, int bit
          tcgen05_skinny_supported(rows, in_features, out_features, bits, dtype, mode);
 }
 
+// Within the small-rows family: one to four tokens on a layer of megabytes go to the CUDA-core
+// GEMV, whose cost per weight is the lowest there.  The gemv tunable set to 0 / 1 forces never /
+// wherever it is supported (for A/B timing).
+bool use_gemv(int64_t rows, int64_t in_features, int64_t out_features, int bits, int dtype, int mode) {
+  const int forced = tunable(OQ_TUNE_GEMV);
+  if (forced == 0 || !gemv_w4_supported(rows, in_features, out_features, bits, dtype, mode)) {
+    return false;
+  }
+  return forced > 0 || out_features * in_features / 2 >= (int64_t(3) << 20);
+}
+
 // Kernel for a problem: the caller's explicit choice, or by shape.
 int choose_kernel(int kernel, int64_t rows, int64_t in_features, int64_t out_features, int bits,
                   int dtype, int mode) {
   if (kernel != OQ_KERNEL_AUTO) {
     return kernel;
+  }
+  if (use_gemv(rows, in_features, out_features, bits, dtype, mode)) {
+    return OQ_KERNEL_SMALL_ROWS;
   }
   const int64_t weight_bytes = out_features * in_features * bits / 8;
   const bool skinny = use_skinny(rows, in_features, out_features, bits, dtype, mode);
@@ -625,6 +644,10 @@ int oq_matmul_packed_weight(void *out, const void *x, int dtype, int64_t rows, i
       if (!small_rows_supported(rows, in_features, out_features, bits, dtype, mode)) {
         return fail(OQ_ERR_UNSUPPORTED, "the small-rows kernel does not take this problem");
       }
+      if (use_gemv(rows, in_features, out_features, bits, dtype, mode)) {
+        return launch_gemv_w4(out, x, rows, in_features, out_features, packed, row_norms_bf16, centroids,
+                              bias, bias_dtype, s);
+      }
       if (use_stream_rows(rows, in_features, out_features, bits, dtype)) {
         return launch_stream_rows(out, x, rows, in_features, out_features, packed, row_norms_bf16,
                                   centroids, bias, bias_dtype, mode, workspace, workspace_bytes, s);
@@ -735,6 +758,9 @@ const char *oq_linear_kernel_name(int64_t rows, int64_t in_features, int64_t out
   const int mode = resolve_weight_mode(weight_mode);
   switch (choose_kernel(kernel, rows, in_features, out_features, weight_bits, dtype, mode)) {
     case OQ_KERNEL_SMALL_ROWS:
+      if (use_gemv(rows, in_features, out_features, weight_bits, dtype, mode)) {
+        return "rotate_quantize + gemv_w4_kernel";
+      }
       if (use_fused_decode(kernel, rows, in_features, out_features, weight_bits, act_bits, dtype, block)) {
         return "decode_fused_kernel";
       }
@@ -812,7 +838,7 @@ int oq_linear_forward(void *out, const void *x, int dtype, int64_t rows, int64_t
                           weight_bits, dtype, mode, row_norms_bf16, weight_centroids, bias,
                           bias_dtype, s);
   }
-  if (chosen == OQ_KERNEL_SMALL_ROWS &&
+  if (chosen == OQ_KERNEL_SMALL_ROWS && !use_gemv(rows, in_features, out_features, weight_bits, dtype, mode) &&
       use_fused_decode(kernel, rows, in_features, out_features, weight_bits, act_bits, dtype, block)) {
     OQ_CHECK_ARG(out && x && packed && row_norms_bf16 && weight_centroids && perm && signs &&
                      act_boundaries && act_centroids, "null device pointer");

@@ -38,6 +38,7 @@ enum {
   OQ_TUNE_PROLOGUE_KERNEL,       // 0 = general, 1 = multi-token CTA, 2 = warp-per-block kernel
   OQ_TUNE_PAIR,                  // large-row tcgen05 kernel: 0 / 1 = never / always the CTA-pair variant
   OQ_TUNE_INT8_MMA,              // INT8-surrogate matmul: 0 = INT8 codes as f16 on the f16 kernel, never kind::i8
+  OQ_TUNE_GEMV,                  // 0 / 1 = never / always the CUDA-core GEMV at one to four tokens
   OQ_TUNE_COUNT
 };
 int tunable(int which);

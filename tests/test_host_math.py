@@ -307,14 +307,17 @@ def test_argument_errors_surface_without_a_gpu():
 
 def test_kernel_plan_by_shape_without_a_gpu():
     """`oq_linear_kernel_name` answers from the shape alone (no launch, no device): the dispatch
-    rules of the forward -- one launch for a few tokens of a small layer, the few-token tensor-core
-    kernel up to 128 rows, the CTA-pair kernel where a 512-row pair tile fills the machine, the
+    rules of the forward -- one launch for a few tokens of a small layer, the CUDA-core GEMV for one
+    to four tokens of a large W4 layer, the few-token tensor-core kernel up to 128 rows, the CTA-pair kernel where a 512-row pair tile fills the machine, the
     single-CTA kernel for 6- and 8-bit weights and for small grids, the general kernel otherwise."""
     from orbitquant_b200 import native
 
     plan = native.forward_kernel_name
     assert plan(1, 768, 2304, 4, 6, 256) == "decode_fused_kernel"
     assert plan(16, 768, 2304, 4, 6, 256) == "rotate_quantize + small_rows_w4_kernel"
+    assert plan(1, 3072, 12288, 4, 4, 1024) == "rotate_quantize + gemv_w4_kernel"
+    assert plan(4, 12288, 3072, 4, 4, 4096) == "rotate_quantize + gemv_w4_kernel"
+    assert plan(5, 12288, 3072, 4, 4, 4096) == "rotate_quantize + skinny_tcgen05_kernel"
     assert plan(16, 3072, 9216, 4, 4, 1024) == "rotate_quantize + skinny_tcgen05_kernel"
     assert plan(128, 3072, 3072, 4, 4, 1024) == "rotate_quantize + skinny_tcgen05_kernel"
     assert plan(300, 768, 512, 4, 4, 256) == "rotate_quantize + gemm_w4_tcgen05_kernel"
