@@ -88,25 +88,6 @@ __device__ __forceinline__ GvWords<KS> gv_load_words(const uint8_t *src) {
   return r;
 }
 
-// The packed words of 8 weight rows for one step (row block, slice) of a warp.
-template <int KS>
-__device__ __forceinline__ void gv_load_rows(GvWords<KS> (&w)[kGvRows], const GemvParams &p, int64_t n0,
-                                             int64_t k0, bool active) {
-  const int64_t row_bytes = p.in_features / 2;
-#pragma unroll
-  for (int r = 0; r < kGvRows; ++r) {
-    const int64_t n = n0 + r;
-    if (active && n < p.out_features) {
-      w[r] = gv_load_words<KS>(p.packed + n * row_bytes + k0 / 2);
-    } else {
-#pragma unroll
-      for (int q = 0; q < KS / 8; ++q) {
-        w[r].w[q] = 0u;
-      }
-    }
-  }
-}
-
 // This lane's KS activations of every token as fp32.
 template <int M, int KS>
 __device__ __forceinline__ void gv_load_x(float (&xr)[M][KS], const GemvParams &p, int64_t k0, bool active) {
@@ -181,19 +162,48 @@ __global__ void __launch_bounds__(gv_cta_warps(M) * 32, 1) gemv_w4_kernel(const 
   // this warp's slices of the reduction dimension and the row blocks of its CTA
   const int s_begin = kw * p.slices_per_warp;
   const int my_slices = min(p.slices, s_begin + p.slices_per_warp) - s_begin;   // >= 1 by construction
-  const int64_t my_blocks =
-      blockIdx.x < p.row_blocks ? (p.row_blocks - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
-  const int64_t steps = my_blocks * my_slices;
-  const int64_t lane_k = static_cast<int64_t>(lane) * KS;
-  constexpr int64_t kSliceElems = 32 * KS;
+  const int my_blocks = blockIdx.x < p.row_blocks
+                            ? static_cast<int>((p.row_blocks - blockIdx.x + gridDim.x - 1) / gridDim.x)
+                            : 0;
+  const int steps = my_blocks * my_slices;
+  const int features = static_cast<int>(p.in_features);
+  const int rows_total = static_cast<int>(p.out_features);
+  const int block_rows_i = p.groups * kGvRows;
+
+  // Where a step's packed words are: every address stays inside the weights -- rows past the end
+  // repeat the last row and lanes past the end of the reduction dimension read its start (their
+  // activations are zero, the rows' results are never stored) -- so the loads need no predicates.
+  // Byte offset of this lane's indices within a row, for slice `sl` of this warp:
+  auto lane_bytes = [&](int sl) -> int {
+    const int k0 = ((s_begin + sl) * 32 + lane) * KS;
+    return k0 < features ? k0 / 2 : 0;
+  };
+  // The 8 rows of block `b` (a multiple of the grid's stride from this CTA's first block).
+  auto load_step = [&](GvWords<KS> (&w)[kGvRows], int b, int sl) {
+    const int n0 = b * block_rows_i + group * kGvRows;
+    const int first = min(n0, rows_total - 1);
+    const uint8_t *ptr = p.packed + static_cast<int64_t>(first) * row_bytes + lane_bytes(sl);
+    const int valid = rows_total - first;   // rows from `first` to the end, >= 1
+    if (valid >= kGvRows) {
+#pragma unroll
+      for (int r = 0; r < kGvRows; ++r) {
+        w[r] = gv_load_words<KS>(ptr);
+        ptr += row_bytes;
+      }
+    } else {
+#pragma unroll
+      for (int r = 0; r < kGvRows; ++r) {
+        w[r] = gv_load_words<KS>(ptr);
+        ptr += r + 1 < valid ? row_bytes : 0;
+      }
+    }
+  };
 
   // the first step's weights are on their way while the table is finished
-  GvWords<KS> w_cur[kGvRows];
-  GvWords<KS> w_nxt[kGvRows];
-  {
-    const int64_t k0 = static_cast<int64_t>(s_begin) * kSliceElems + lane_k;
-    gv_load_rows<KS>(w_cur, p, static_cast<int64_t>(blockIdx.x) * block_rows + group * kGvRows, k0,
-                     steps > 0 && k0 < p.in_features);
+  GvWords<KS> w_a[kGvRows];
+  GvWords<KS> w_b[kGvRows];
+  if (steps > 0) {
+    load_step(w_a, static_cast<int>(blockIdx.x), 0);
   }
   __syncthreads();
   // the activations are read from here on
@@ -208,9 +218,12 @@ __global__ void __launch_bounds__(gv_cta_warps(M) * 32, 1) gemv_w4_kernel(const 
     }
   }
   float xr[M][KS];
+  auto load_x = [&](int sl) {
+    const int k0 = ((s_begin + sl) * 32 + lane) * KS;
+    gv_load_x<M, KS>(xr, p, k0, k0 < features);
+  };
   if (my_slices == 1) {   // one slice per warp: its activations never change
-    const int64_t k0 = static_cast<int64_t>(s_begin) * kSliceElems + lane_k;
-    gv_load_x<M, KS>(xr, p, k0, k0 < p.in_features);
+    load_x(0);
   }
 
   // entry v of this lane's copy of the table: byte 1 of this address replaced by v
@@ -231,32 +244,30 @@ __global__ void __launch_bounds__(gv_cta_warps(M) * 32, 1) gemv_w4_kernel(const 
   float out_norm = 0.0f;
   float out_bias = 0.0f;
   if (threadIdx.x < outputs) {
-    const int64_t n = static_cast<int64_t>(blockIdx.x) * block_rows + out_row;
-    if (n < p.out_features) {
+    const int n = static_cast<int>(blockIdx.x) * block_rows_i + out_row;
+    if (n < rows_total) {
       out_norm = __bfloat162float(p.row_norms[n]);
       out_bias = p.bias_dtype >= 0 ? gv_bias(p.bias, p.bias_dtype, n) : 0.0f;
     }
   }
 
-  int64_t blk = blockIdx.x;
+  int blk = static_cast<int>(blockIdx.x);
   int sl = 0;
   int parity = 0;
-  for (int64_t t = 0; t < steps; ++t) {
-    // the next step's weights first, so that they arrive under this step's arithmetic
+  // One step: the next step's packed words first, so that they arrive under this step's
+  // arithmetic, then 8 rows x KS indices of this step.
+  auto step = [&](GvWords<KS> (&cur)[kGvRows], GvWords<KS> (&nxt)[kGvRows], bool more) {
     int next_sl = sl + 1;
-    int64_t next_blk = blk;
+    int next_blk = blk;
     if (next_sl == my_slices) {
       next_sl = 0;
-      next_blk += gridDim.x;
+      next_blk += static_cast<int>(gridDim.x);
     }
-    {
-      const int64_t k0 = static_cast<int64_t>(s_begin + next_sl) * kSliceElems + lane_k;
-      gv_load_rows<KS>(w_nxt, p, next_blk * block_rows + group * kGvRows, k0,
-                       t + 1 < steps && k0 < p.in_features);
+    if (more) {
+      load_step(nxt, next_blk, next_sl);
     }
     if (my_slices > 1) {
-      const int64_t k0 = static_cast<int64_t>(s_begin + sl) * kSliceElems + lane_k;
-      gv_load_x<M, KS>(xr, p, k0, k0 < p.in_features);
+      load_x(sl);
     }
 
     // byte by byte, the 8 rows interleaved: 8 * M independent accumulation chains
@@ -267,7 +278,7 @@ __global__ void __launch_bounds__(gv_cta_warps(M) * 32, 1) gemv_w4_kernel(const 
 #pragma unroll
         for (int r = 0; r < kGvRows; ++r) {
           // one byte permute: bytes 0, 2, 3 of the lane's base address, byte 1 = packed byte j
-          const float2 e = gv_lds_f32x2(__byte_perm(lane_base, w_cur[r].w[q], 0x3240 + 0x10 * j));
+          const float2 e = gv_lds_f32x2(__byte_perm(lane_base, cur[r].w[q], 0x3240 + 0x10 * j));
 #pragma unroll
           for (int m = 0; m < M; ++m) {
             acc[r][m] = fmaf(e.x, xr[m][8 * q + 2 * j], acc[r][m]);
@@ -319,8 +330,8 @@ __global__ void __launch_bounds__(gv_cta_warps(M) * 32, 1) gemv_w4_kernel(const 
       __syncthreads();
       // the slices of a row in slice order, then row norm and bias
       if (threadIdx.x < outputs) {
-        const int64_t n = blk * block_rows + out_row;
-        if (n < p.out_features) {
+        const int n = blk * block_rows_i + out_row;
+        if (n < rows_total) {
           float sum = 0.0f;
           for (int k = 0; k < p.ksplit; ++k) {
             sum = __fadd_rn(sum, part[((out_g * p.ksplit + k) * kGvRows + out_r) * M + out_m]);
@@ -330,20 +341,23 @@ __global__ void __launch_bounds__(gv_cta_warps(M) * 32, 1) gemv_w4_kernel(const 
               __float2bfloat16_rn(sum);
         }
         // the next block's row norm and bias, long before they are needed
-        const int64_t next_n = (blk + gridDim.x) * block_rows + out_row;
-        if (next_n < p.out_features) {
+        const int next_n = (blk + static_cast<int>(gridDim.x)) * block_rows_i + out_row;
+        if (next_n < rows_total) {
           out_norm = __bfloat162float(p.row_norms[next_n]);
           out_bias = p.bias_dtype >= 0 ? gv_bias(p.bias, p.bias_dtype, next_n) : 0.0f;
         }
       }
       parity ^= 1;
     }
-#pragma unroll
-    for (int r = 0; r < kGvRows; ++r) {
-      w_cur[r] = w_nxt[r];
-    }
     sl = next_sl;
     blk = next_blk;
+  };
+  // two steps per trip: the two sets of packed words swap roles without being copied
+  for (int t = 0; t < steps; t += 2) {
+    step(w_a, w_b, t + 1 < steps);
+    if (t + 1 < steps) {
+      step(w_b, w_a, t + 2 < steps);
+    }
   }
 }
 
