@@ -775,9 +775,15 @@ def main():
                 decode[f"M={m}"] = measure_decode("vit_decode", m, device, 20, 3, with_e2e=False)
             except Exception as exc:  # the headline stands on its own
                 decode[f"M={m}"] = {"error": f"{type(exc).__name__}: {exc}"}
+        try:
+            # the same pass on the DiT block's own layers at one token: the CUDA-core GEMV
+            decode["dit_block M=1"] = measure_decode("dit_block", 1, device, 10, 3, with_e2e=False)
+        except Exception as exc:
+            decode["dit_block M=1"] = {"error": f"{type(exc).__name__}: {exc}"}
         line["decode"] = {"metric": "orbitlinear_decode_hbm_gbs", "unit": "GB/s",
-                          "what": "ViT-base W4A6, 12 blocks x 4 projections in one CUDA graph, weights "
-                                  "cold in L2 (several weight sets > 2x L2 walked per replay)",
+                          "what": "ViT-base W4A6 (and, last case, the DiT block's W4A4 layers), 12 blocks x 4 "
+                                  "projections in one CUDA graph, weights cold in L2 (several weight sets "
+                                  "> 2x L2 walked per replay)",
                           "cases": decode}
         others = {}
         for name in ("single_layer", "mixed_bit", "video_dit"):

@@ -411,12 +411,9 @@ int launch_gemv_rows(GemvParams p, cudaStream_t stream) {
   if (best < 0.0) {
     return fail(OQ_ERR_UNSUPPORTED, "the GEMV kernel found no split for this problem");
   }
-  static bool attribute_set[4] = {false, false, false, false};
-  if (!attribute_set[M - 1]) {
-    OQ_CHECK_CUDA(cudaFuncSetAttribute(gemv_w4_kernel<M, KS>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                       kGvSmemBytes));
-    attribute_set[M - 1] = true;
-  }
+  // per device and cheap: set at every launch, like the other kernels' attributes
+  OQ_CHECK_CUDA(cudaFuncSetAttribute(gemv_w4_kernel<M, KS>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                     kGvSmemBytes));
   cudaLaunchConfig_t config = {};
   config.gridDim = dim3(static_cast<unsigned>(best_grid));
   config.blockDim = dim3(static_cast<unsigned>(kWarps * 32));
