@@ -361,13 +361,12 @@ __global__ void __launch_bounds__(gv_cta_warps(M) * 32, 1) gemv_w4_kernel(const 
   }
 }
 
-// Reduction indices per lane and slice, by token count: what keeps the kernel within its
-// register budget (activations of M tokens + two sets of packed words of 8 rows + 8 * M sums).
-constexpr int gv_ks(int rows) { return rows == 1 ? 16 : 8; }
-
-template <int M>
+// Reduction indices per lane and slice: 8 keep the kernel within its register budget at every
+// token count (activations of M tokens + two sets of packed words of 8 rows + 8 * M sums); one
+// token has room for 16, which halves the steps and measures faster up to K = 8192 (9.1 against
+// 10.1 us on 3072 -> 9216; beyond, 8 is faster: 10.4 against 11.7 us on 12288 -> 3072).
+template <int M, int KS>
 int launch_gemv_rows(GemvParams p, cudaStream_t stream) {
-  constexpr int KS = gv_ks(M);
   constexpr int kWarps = gv_cta_warps(M);
   static_assert(2 * kWarps * kGvRows * M * sizeof(float) <= kGvPartBytes, "per-warp sums fit beside the table");
   int device = 0;
@@ -453,10 +452,11 @@ int launch_gemv_w4(void *out, const void *x, int64_t rows, int64_t in_features, 
   p.in_features = in_features;
   p.out_features = out_features;
   switch (rows) {
-    case 1: return launch_gemv_rows<1>(p, stream);
-    case 2: return launch_gemv_rows<2>(p, stream);
-    case 3: return launch_gemv_rows<3>(p, stream);
-    case 4: return launch_gemv_rows<4>(p, stream);
+    case 1:
+      return in_features < 8192 ? launch_gemv_rows<1, 16>(p, stream) : launch_gemv_rows<1, 8>(p, stream);
+    case 2: return launch_gemv_rows<2, 8>(p, stream);
+    case 3: return launch_gemv_rows<3, 8>(p, stream);
+    case 4: return launch_gemv_rows<4, 8>(p, stream);
     default: return fail(OQ_ERR_UNSUPPORTED, "the GEMV kernel takes one to four tokens");
   }
 }
