@@ -606,8 +606,10 @@ def kernel_alone(layers, inputs, steps, peaks):
 
 
 def measure_single_gpu(workload, device, steps, warmup, rows_override=0, on_device=False,
-                       with_kernel=True, sustained=True, weight_mode=None):
-    """value / ms_per_step of a large-row workload on one GPU, resident inputs."""
+                       with_kernel=True, sustained=True, weight_mode=None, graph=False):
+    """value / ms_per_step of a large-row workload on one GPU, resident inputs.  With `graph` the
+    step is captured once in a CUDA graph and replayed (for routes whose host-side call is long
+    next to their kernels)."""
     from orbitquant_b200 import native
 
     rows, layers, spec = build_layers(workload, device, rows_override=rows_override, on_device=on_device,
@@ -627,9 +629,27 @@ def measure_single_gpu(workload, device, steps, warmup, rows_override=0, on_devi
 
     for _ in range(max(3, warmup)):
         step()
-    launches0 = native.launch_count()
-    elapsed_ms = time_steps(step, steps, barrier)
-    launches = native.launch_count() - launches0
+    if graph:
+        eager_step = step
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            eager_step()
+        torch.cuda.current_stream().wait_stream(side)
+        captured = torch.cuda.CUDAGraph()
+        launches0 = native.launch_count()
+        with torch.cuda.graph(captured):
+            eager_step()
+        per_step = native.launch_count() - launches0
+        step = captured.replay
+        for _ in range(3):
+            step()
+        elapsed_ms = time_steps(step, steps, barrier)
+        launches = per_step * steps
+    else:
+        launches0 = native.launch_count()
+        elapsed_ms = time_steps(step, steps, barrier)
+        launches = native.launch_count() - launches0
     ms_per_step = elapsed_ms / steps
     flops = sum(layer_flops(rows, l.k, l.n) for l, _m in layers)
     result = {"workload": describe(workload, spec, rows), "value": flops / (ms_per_step * 1e-3) / 1e12,
@@ -801,13 +821,14 @@ def main():
             # construction, so it is reported beside the headline, never as it
             res, l_, i_, _s = measure_single_gpu("dit_block", device, extras_steps, 3, on_device=True,
                                                  sustained=False, with_kernel=False,
-                                                 weight_mode="int8_surrogate")
+                                                 weight_mode="int8_surrogate", graph=True)
             backends = sorted({m.last_activation_kernel_backend for _l, m in l_})
             del l_, i_
             torch.cuda.empty_cache()
             res["unit"] = "T-op/s"
             res["what"] = ("weight_mode int8_surrogate: rotate + quantise to INT8 codes, "
-                           "tcgen05.mma kind::i8 with int32 accumulation; 2*M*K*N operations per layer")
+                           "tcgen05.mma kind::i8 with int32 accumulation; 2*M*K*N operations per layer; "
+                           "the step captured in a CUDA graph and replayed")
             res["backends"] = backends
             res.pop("frac_of_burst", None)
             res.pop("frac_of_sustained", None)
