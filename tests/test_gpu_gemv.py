@@ -18,6 +18,8 @@ CASES = [
     (4, 3072, 3072, 6, True, False), (1, 12288, 1024, 4, True, False), (4, 5120, 1536, 4, True, False),
     (1, 256, 8, 4, True, True), (2, 1280, 77, 3, True, True), (3, 768, 2304, 6, False, True),
     (4, 2304, 1003, 4, True, True), (1, 13824, 520, 4, True, False),
+    # several passes of the persistent grid over the row blocks, the last block ragged
+    (1, 3072, 12296, 4, True, False), (2, 1024, 9740, 4, False, True),
 ]
 
 
