@@ -58,6 +58,7 @@ def _forward_static(module: OrbitQuantLinear, x: torch.Tensor, kernel: int = 0,
     (16, 3072, 3072, 4, 4, True, "tcgen05"),  # few-token kernel, several reduction slices: partial
                                               # sums and slice COUNTERS live in the shared array
     (96, 1024, 640, 4, 4, False, "tcgen05"),  # explicit kernel choice, no bias
+    (2, 3072, 3072, 4, 4, True, "auto"),       # two tokens of a large layer: prologue + CUDA-core GEMV
 ])
 def test_static_scratch_forward_matches_workspace_forward(rows, k, n, w_bits, a_bits, bias, kernel):
     if not torch.cuda.is_available():
