@@ -434,7 +434,8 @@ int launch_gemv_rows(GemvParams p, cudaStream_t stream) {
 bool gemv_w4_supported(int64_t rows, int64_t in_features, int64_t out_features, int bits, int dtype,
                        int weight_mode) {
   return rows >= 1 && rows <= 4 && bits == 4 && dtype == OQ_DTYPE_BF16 && weight_mode != OQ_WEIGHT_BF16_SCALED &&
-         out_features >= 1 && in_features >= 256 && in_features % 256 == 0 && in_features <= (1 << 24);
+         out_features >= 1 && out_features <= (1 << 28) && in_features >= 256 && in_features % 256 == 0 &&
+         in_features <= (1 << 24);   // row and feature numbers are 32-bit inside the kernel
 }
 
 int launch_gemv_w4(void *out, const void *x, int64_t rows, int64_t in_features, int64_t out_features,
