@@ -707,6 +707,9 @@ def main():
     parser.add_argument("--warmup", type=int, default=5)
     parser.add_argument("--impl", default="ours", choices=["ours", "reference"])
     parser.add_argument("--workload", default="dit_block", choices=WORKLOAD_NAMES)
+    parser.add_argument("--weight-mode", default="auto", choices=["auto", "int8_surrogate"],
+                        help="one GPU, large batches: int8_surrogate runs the workload through the "
+                             "integer route (approximate by construction; T-op/s, no kernel-alone pass)")
     parser.add_argument("--no-cpu-baseline", action="store_true")
     parser.add_argument("--no-extras", action="store_true",
                         help="one GPU: skip the decode and other-configuration measurements")
@@ -742,8 +745,12 @@ def main():
     warmup = max(3, args.warmup)
     sampler = ClockSampler(local_rank)
     sampler.start()
+    integer_route = args.weight_mode == "int8_surrogate"
     result, layers, inputs, spec = measure_single_gpu(args.workload, device, args.steps, warmup,
-                                                      rows_override=args.rows)
+                                                      rows_override=args.rows,
+                                                      with_kernel=not integer_route,
+                                                      weight_mode="int8_surrogate" if integer_route else None,
+                                                      graph=integer_route)
     clocks = sampler.stop()
     rows = inputs[0].shape[0]
 
@@ -755,23 +762,30 @@ def main():
                                            lambda: torch.cuda.synchronize(), use_graph=True)
     total_flops = sum(layer_flops(rows, l.k, l.n) for l, _m in layers)
 
-    roofline = result["roofline"]
-    roofline["traffic"] = NCU_TRAFFIC_BYTES.get(args.workload) if not args.rows else None
+    roofline = result.get("roofline")
+    if roofline is not None:
+        roofline["traffic"] = NCU_TRAFFIC_BYTES.get(args.workload) if not args.rows else None
     line = {
-        "metric": "orbitlinear_tflops", "value": result["value"], "unit": "TFLOP/s", "n_gpus": 1,
+        "metric": "orbitlinear_tflops", "value": result["value"],
+        "unit": "T-op/s" if integer_route else "TFLOP/s", "n_gpus": 1,
         "steps": args.steps, "warmup": warmup, "ms_per_step": result["ms_per_step"],
-        "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "bf16",
+        "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+        "dtype": "int8 (int32 accumulation)" if integer_route else "bf16",
         "data": "synthetic",
         "config": {
             "workload": result["workload"],
             "l2": "per-step working set (inputs+weights+outputs) exceeds the 126 MB L2; no flush",
             "parallelism": "single", "gather": None,
-            "weight_mode": "centroid (f16 centroid operand, row norm in the epilogue)",
+            "weight_mode": ("int8_surrogate (INT8 code operands on tcgen05.mma kind::i8; approximate by "
+                            "construction; the step replayed from a CUDA graph)" if integer_route else
+                            "centroid (f16 centroid operand, row norm in the epilogue)"),
             "cpu_sample": cpu_sample_note(args.workload),
         },
         "roofline": roofline,
-        "forward": {"frac_of_burst": result["frac_of_burst"], "frac_of_sustained": result["frac_of_sustained"],
-                    "what": "value / measured cuBLAS bf16 peak: prologue + GEMM of every projection"},
+        # fractions of the bf16 peaks say nothing about integer operations
+        "forward": None if integer_route else {
+            "frac_of_burst": result["frac_of_burst"], "frac_of_sustained": result["frac_of_sustained"],
+            "what": "value / measured cuBLAS bf16 peak: prologue + GEMM of every projection"},
         "sustained": result.get("sustained"),
         "e2e": {"value": total_flops / (e2e_ms / e2e_steps * 1e-3) / 1e12, "unit": "TFLOP/s",
                 "h2d_bytes_per_step": host_x.numel() * 2, "d2h_bytes_per_step": host_y.numel() * 2,
@@ -787,7 +801,10 @@ def main():
     del layers, inputs, chain
     torch.cuda.empty_cache()
 
-    if not args.no_extras and args.workload == "dit_block" and not args.rows:
+    if integer_route and line["sustained"]:
+        line["sustained"]["unit"] = "T-op/s"
+        line["sustained"].pop("frac_of_sustained_peak", None)
+    if not args.no_extras and args.workload == "dit_block" and not args.rows and not integer_route:
         extras_steps = max(5, min(args.steps, 10))
         decode = {}
         for m in (1, 4, 16):
