@@ -214,8 +214,10 @@ int oq_rows_to_f16_operand(const void *x, int dtype, int64_t rows, int64_t dim, 
  * reference's fit_int8_centroid_surrogate (src/orbitquant/kernels/triton_cuda.py:1826-1857).
  * Replaces matmul_packed_w4a4_int8 (packed_matmul.cu:744-1009, host :1715-1892) and the
  * fused Triton kernels (triton_cuda.py:1861-2099).  Approximate by construction (the codes
- * are rounded centroids); the integer contraction itself is exact: it runs on the f16 tensor
- * cores, where INT8 codes, their products and sums below 2^24 are exact.
+ * are rounded centroids); the integer contraction itself is exact: above 128 rows of a 4-bit
+ * layer with in_features % 128 == 0 it runs on the INT8 tensor-core instructions with int32
+ * accumulators (tunable int8_mma = 0 switches that off), otherwise on the f16 tensor cores,
+ * where INT8 codes, their products and sums below 2^24 are exact.
  * Three launches (code table, operand expansion, GEMM); in_features % 64 == 0. */
 size_t oq_matmul_packed_w4a4_int8_workspace_bytes(int64_t rows, int64_t in_features);
 int oq_matmul_packed_w4a4_int8(void *out, const uint8_t *packed_act, const uint8_t *packed_weight,
